@@ -1,0 +1,518 @@
+// Host side of the C ABI declared in include/flashmoe_b200.h: validation, allocation of the
+// symmetric block and the private workspace, CUDA-IPC peer mapping, TMA descriptor
+// construction and the launches.  It plays the role of the reference's bootstrap
+// (csrc/include/flashmoe/bootstrap.cuh:197-474) and of its pybind glue
+// (flashmoe/bindings.py:68-185, 238-315), with CUDA IPC in place of the NVSHMEM heap.
+#include <cstdio>
+#include <cstring>
+#include <new>
+#include <string>
+#include <vector>
+
+#include "common.cuh"
+
+namespace fmoe {
+namespace {
+
+thread_local std::string t_error;
+
+int set_error(int code, const std::string& msg) {
+  t_error = msg;
+  return code;
+}
+
+#define FMOE_CUDA(expr)                                                                      \
+  do {                                                                                       \
+    cudaError_t err__ = (expr);                                                              \
+    if (err__ != cudaSuccess) {                                                              \
+      return set_error(FMOE_ERR_CUDA, std::string(#expr) + ": " + cudaGetErrorName(err__) +  \
+                                          " (" + cudaGetErrorString(err__) + ")");           \
+    }                                                                                        \
+  } while (0)
+
+size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn == nullptr) {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) ==
+            cudaSuccess && q == cudaDriverEntryPointSuccess) {
+      fn = reinterpret_cast<EncodeTiledFn>(sym);
+    }
+  }
+  return fn;
+}
+
+// 2-D row-major [rows, cols] 16-bit tensor, box = 64 columns x 128 rows, 128-byte swizzle.
+int make_map(CUtensorMap* out, int ab_format, const void* base, uint64_t rows, uint64_t cols) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (fn == nullptr) return set_error(FMOE_ERR_CUDA, "cuTensorMapEncodeTiled is not available");
+  const cuuint64_t dims[2] = {cols, rows};
+  const cuuint64_t strides[1] = {cols * 2};
+  const cuuint32_t box[2] = {static_cast<cuuint32_t>(kTileK), 128};
+  const cuuint32_t elem[2] = {1, 1};
+  const CUresult r = fn(out, ab_format == 1 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16,
+                        2, const_cast<void*>(base), dims, strides, box, elem,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                        CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    return set_error(FMOE_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult " + std::to_string(r) +
+                                        " (base must be 16-byte aligned, row pitch a multiple of 16 bytes)");
+  }
+  return FMOE_OK;
+}
+
+}  // namespace
+}  // namespace fmoe
+
+using namespace fmoe;
+
+struct fmoe_ctx {
+  fmoe_model_desc model{};
+  int W = 1, rank = 0, nLx = 0, device = 0;
+  std::vector<int32_t> owner, lidx, local_e;
+  fmoe_geometry geo{};
+  SymmLayout lay{};
+  char* symm = nullptr;                 // this rank's block
+  char* peers[FMOE_MAX_WORLD] = {};     // mapped blocks (peers[rank] == symm)
+  bool imported[FMOE_MAX_WORLD] = {};   // opened through IPC (must be closed)
+  bool committed = false;
+  char* work = nullptr;                 // private workspace, one allocation
+  size_t work_bytes = 0;
+  MoeParams params{};                   // everything but the per-forward pointers
+  CUtensorMap maps[5];
+  const void* map_src[3] = {nullptr, nullptr, nullptr};  // up, up_v, down the maps were built for
+  void* stage_tokens = nullptr;         // host-buffer entry point staging
+  void* stage_out = nullptr;
+};
+
+struct fmoe_router {
+  fmoe_model_desc model{};
+  int device = 0;
+  int return_logits = 0;
+  int32_t* topk_idx = nullptr;
+  float* topk_w = nullptr;
+};
+
+namespace {
+
+int validate_model(const fmoe_model_desc* m) {
+  if (m == nullptr) return set_error(FMOE_ERR_INVALID_ARG, "model description is null");
+  if (m->gpu_arch != 1000 && m->gpu_arch != 1030)
+    return set_error(FMOE_ERR_UNSUPPORTED, "gpu_arch " + std::to_string(m->gpu_arch) +
+                                               " is not supported: this library is built for sm_100a only "
+                                               "(pass 1000)");
+  if (m->tokens_per_rank < 1 || m->token_dim < 1 || m->ffn_size < 1 || m->num_experts < 1 || m->top_k < 1)
+    return set_error(FMOE_ERR_INVALID_ARG, "S, H, I, E and k must be positive");
+  if (m->top_k > m->num_experts || m->top_k > 32)
+    return set_error(FMOE_ERR_INVALID_ARG, "top_k must not exceed num_experts (or 32)");
+  if (m->expert_peer_capacity < 1)
+    return set_error(FMOE_ERR_INVALID_ARG, "expert_peer_capacity must be positive");
+  if (m->num_experts % 8 != 0)
+    return set_error(FMOE_ERR_INVALID_ARG, "num_experts must be a multiple of 8");
+  if (m->token_dim % kTileK != 0)
+    return set_error(FMOE_ERR_INVALID_ARG, "token dimension should be multiples of tile dimensions (64)");
+  if (m->ffn_size % kTileK != 0)
+    return set_error(FMOE_ERR_INVALID_ARG, "Intermediate size should be multiples of tile dimensions (64)");
+  if (m->mlp_type != FMOE_MLP_GATED && m->mlp_type != FMOE_MLP_VANILLA)
+    return set_error(FMOE_ERR_INVALID_ARG, "unknown mlp_type");
+  if (m->act_type < FMOE_ACT_IDENTITY || m->act_type > FMOE_ACT_RELU)
+    return set_error(FMOE_ERR_INVALID_ARG, "unknown act_type");
+  if (m->data_type < FMOE_DT_BF16 || m->data_type > FMOE_DT_FP64)
+    return set_error(FMOE_ERR_INVALID_ARG, "elementBytes not supported");
+  if (static_cast<long long>(m->tokens_per_rank) * m->top_k >= (1LL << kMetaSrcShift))
+    return set_error(FMOE_ERR_UNSUPPORTED, "tokens_per_rank * top_k must stay below 2^26");
+  return FMOE_OK;
+}
+
+void free_ctx(fmoe_ctx* c) {
+  if (c == nullptr) return;
+  for (int r = 0; r < FMOE_MAX_WORLD; ++r)
+    if (c->imported[r] && c->peers[r] != nullptr) cudaIpcCloseMemHandle(c->peers[r]);
+  if (c->symm) cudaFree(c->symm);
+  if (c->work) cudaFree(c->work);
+  if (c->stage_tokens) cudaFree(c->stage_tokens);
+  if (c->stage_out) cudaFree(c->stage_out);
+  delete c;
+}
+
+}  // namespace
+
+extern "C" {
+
+const char* fmoe_strerror(int code) {
+  switch (code) {
+    case FMOE_OK: return "success";
+    case FMOE_ERR_INVALID_ARG: return "invalid argument";
+    case FMOE_ERR_UNSUPPORTED: return "unsupported configuration";
+    case FMOE_ERR_CUDA: return "CUDA call failed";
+    case FMOE_ERR_NOT_READY: return "context not ready (peers missing or not committed)";
+    case FMOE_ERR_DEVICE_TIMEOUT: return "a device-side wait ran out";
+    case FMOE_ERR_NO_MEMORY: return "out of memory";
+    default: return "unknown status";
+  }
+}
+
+const char* fmoe_last_error(void) { return t_error.c_str(); }
+
+uint64_t fmoe_launch_count(void) { return g_launches; }
+
+int fmoe_ctx_create(const fmoe_model_desc* model, const fmoe_ep_desc* ep, void* stream, fmoe_ctx** out) {
+  if (out == nullptr) return set_error(FMOE_ERR_INVALID_ARG, "out is null");
+  *out = nullptr;
+  int rc = validate_model(model);
+  if (rc != FMOE_OK) return rc;
+  if (ep == nullptr) return set_error(FMOE_ERR_INVALID_ARG, "ep description is null");
+  if (model->data_type != FMOE_DT_BF16 && model->data_type != FMOE_DT_FP16)
+    return set_error(FMOE_ERR_UNSUPPORTED, "the expert kernels handle BF16 and FP16; FP32/FP64 are not built yet");
+  if (ep->topology != FMOE_TOPO_NVLINK_ONLY)
+    return set_error(FMOE_ERR_UNSUPPORTED, "only Topology.NVLINK_ONLY (one NVLink box) is implemented");
+  const int W = ep->ep_world, E = model->num_experts;
+  if (W < 1 || W > FMOE_MAX_WORLD)
+    return set_error(FMOE_ERR_UNSUPPORTED, "ep_world must be between 1 and " + std::to_string(FMOE_MAX_WORLD));
+  if (ep->ep_rank < 0 || ep->ep_rank >= W) return set_error(FMOE_ERR_INVALID_ARG, "ep_rank out of range");
+  if (ep->expert_map == nullptr || ep->rank_map == nullptr)
+    return set_error(FMOE_ERR_INVALID_ARG, "expert_map and rank_map are required");
+  if (ep->num_local_experts < 1 || ep->num_local_experts * W != E)
+    return set_error(FMOE_ERR_INVALID_ARG, "every rank must hold num_experts / ep_world experts");
+  const int nLx = ep->num_local_experts;
+  if (static_cast<long long>(W) * E > 4096)
+    return set_error(FMOE_ERR_UNSUPPORTED, "ep_world * num_experts must not exceed 4096");
+
+  fmoe_ctx* c = new (std::nothrow) fmoe_ctx();
+  if (c == nullptr) return set_error(FMOE_ERR_NO_MEMORY, "host allocation failed");
+  c->model = *model;
+  c->W = W; c->rank = ep->ep_rank; c->nLx = nLx; c->device = ep->device_id;
+  c->owner.assign(ep->expert_map, ep->expert_map + E);
+  c->lidx.assign(E, 0);
+  c->local_e.assign(static_cast<size_t>(W) * nLx, -1);
+  std::vector<int> fill(W, 0);
+  for (int e = 0; e < E; ++e) {
+    const int r = c->owner[e];
+    if (r < 0 || r >= W || fill[r] >= nLx) {
+      free_ctx(c);
+      return set_error(FMOE_ERR_INVALID_ARG, "expert_map must give every rank exactly num_local_experts experts");
+    }
+    c->lidx[e] = fill[r];
+    c->local_e[static_cast<size_t>(r) * nLx + fill[r]] = e;
+    ++fill[r];
+  }
+
+  cudaError_t ce = cudaSetDevice(c->device);
+  if (ce != cudaSuccess) { free_ctx(c); return set_error(FMOE_ERR_CUDA, std::string("cudaSetDevice: ") + cudaGetErrorString(ce)); }
+  int sms = 0, cc_major = 0;
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, c->device);
+  cudaDeviceGetAttribute(&cc_major, cudaDevAttrComputeCapabilityMajor, c->device);
+  if (cc_major != 10) { free_ctx(c); return set_error(FMOE_ERR_UNSUPPORTED, "device is not compute capability 10.x"); }
+
+  const int S = model->tokens_per_rank, H = model->token_dim, I = model->ffn_size, k = model->top_k;
+  const int EC = model->expert_peer_capacity;
+  const bool gated = model->mlp_type == FMOE_MLP_GATED;
+  fmoe_geometry& g = c->geo;
+  g.tile_m = kTileM; g.tile_k = kTileK; g.stages = kStages;
+  g.tile_n0 = gated ? 128 : 256; g.tile_n1 = 256;
+  g.round_ec = static_cast<int>(align_up(EC, kTileM));
+  const long long cap_a = static_cast<long long>(nLx) * align_up(static_cast<size_t>(W) * EC, kTileM);
+  const long long cap_b = static_cast<long long>(align_up(static_cast<size_t>(W) * S * k, kTileM)) +
+                          static_cast<long long>(nLx) * kTileM;
+  g.landing_rows = static_cast<int>(cap_a < cap_b ? cap_a : cap_b);
+  g.grid = sms; g.threads = kThreads;
+  g.smem_bytes = static_cast<int>(moe_smem_bytes(W, E, nLx));
+  if (g.smem_bytes > 227 * 1024) { free_ctx(c); return set_error(FMOE_ERR_UNSUPPORTED, "tables do not fit in shared memory"); }
+
+  // symmetric block layout (same arithmetic on every rank)
+  SymmLayout& L = c->lay;
+  size_t off = 0;
+  L.cnt_table = off; off = align_up(off + sizeof(int32_t) * 2 * W * E, 256);
+  L.cnt_flag = off; off = align_up(off + sizeof(uint64_t) * 2 * W, 256);
+  L.disp_arrived = off; off = align_up(off + sizeof(uint32_t) * W * nLx, 256);
+  L.ret_arrived = off; off = align_up(off + sizeof(uint32_t), 256);
+  L.landing_meta = off; off = align_up(off + sizeof(uint32_t) * g.landing_rows, 1024);
+  L.landing = off; off = align_up(off + static_cast<size_t>(g.landing_rows) * H * 2, 1024);
+  L.ret = off; off = align_up(off + static_cast<size_t>(S) * k * H * 2, 1024);
+  L.total = off;
+  g.symm_bytes = static_cast<int64_t>(L.total);
+
+  ce = cudaMalloc(&c->symm, L.total);
+  if (ce != cudaSuccess) { free_ctx(c); return set_error(FMOE_ERR_NO_MEMORY, std::string("symmetric block: ") + cudaGetErrorString(ce)); }
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  // control words must start at zero; the data areas need no initial value
+  ce = cudaMemsetAsync(c->symm, 0, L.landing, st);
+  if (ce != cudaSuccess) { free_ctx(c); return set_error(FMOE_ERR_CUDA, cudaGetErrorString(ce)); }
+  c->peers[c->rank] = c->symm;
+
+  // private workspace
+  const int max_mtiles = g.landing_rows / kTileM;
+  size_t w = 0;
+  const size_t w_y = w; w = align_up(w + static_cast<size_t>(g.landing_rows) * I * 2, 1024);
+  const size_t w_done = w; w = align_up(w + sizeof(uint32_t) * max_mtiles, 256);
+  const size_t w_ctl = w; w = align_up(w + 256, 256);   // ticket, done_ctas, abort, epoch
+  const size_t w_status = w; w = align_up(w + sizeof(fmoe_status), 256);
+  const size_t w_table = w; w = align_up(w + sizeof(TokenSlot) * E * g.round_ec, 256);
+  const size_t w_routes = w; w = align_up(w + sizeof(Route) * S * k, 256);
+  const size_t w_owner = w; w = align_up(w + sizeof(int32_t) * E, 256);
+  const size_t w_lidx = w; w = align_up(w + sizeof(int32_t) * E, 256);
+  const size_t w_local = w; w = align_up(w + sizeof(int32_t) * W * nLx, 256);
+  c->work_bytes = w;
+  g.workspace_bytes = static_cast<int64_t>(w);
+  ce = cudaMalloc(&c->work, w);
+  if (ce != cudaSuccess) { free_ctx(c); return set_error(FMOE_ERR_NO_MEMORY, std::string("workspace: ") + cudaGetErrorString(ce)); }
+  ce = cudaMemsetAsync(c->work + w_done, 0, w - w_done, st);
+  if (ce == cudaSuccess) ce = cudaMemcpyAsync(c->work + w_owner, c->owner.data(), sizeof(int32_t) * E, cudaMemcpyHostToDevice, st);
+  if (ce == cudaSuccess) ce = cudaMemcpyAsync(c->work + w_lidx, c->lidx.data(), sizeof(int32_t) * E, cudaMemcpyHostToDevice, st);
+  if (ce == cudaSuccess) ce = cudaMemcpyAsync(c->work + w_local, c->local_e.data(), sizeof(int32_t) * W * nLx, cudaMemcpyHostToDevice, st);
+  if (ce == cudaSuccess) ce = cudaStreamSynchronize(st);
+  if (ce == cudaSuccess) ce = moe_prepare_kernel(g.smem_bytes);
+  if (ce != cudaSuccess) { free_ctx(c); return set_error(FMOE_ERR_CUDA, std::string("workspace set-up: ") + cudaGetErrorString(ce)); }
+
+  MoeParams& p = c->params;
+  p.S = S; p.H = H; p.I = I; p.E = E; p.k = k; p.EC = EC; p.round_ec = g.round_ec;
+  p.W = W; p.rank = c->rank; p.nLx = nLx;
+  p.gated = gated ? 1 : 0; p.act = model->act_type; p.ab_format = model->data_type == FMOE_DT_BF16 ? 1 : 0;
+  p.tiles_n0 = (I + g.tile_n0 - 1) / g.tile_n0;
+  p.tiles_n1 = (H + g.tile_n1 - 1) / g.tile_n1;
+  p.landing_rows = g.landing_rows; p.max_mtiles = max_mtiles;
+  p.owner = reinterpret_cast<const int32_t*>(c->work + w_owner);
+  p.lidx = reinterpret_cast<const int32_t*>(c->work + w_lidx);
+  p.local_e = reinterpret_cast<const int32_t*>(c->work + w_local);
+  p.lay = L;
+  p.y = c->work + w_y;
+  p.gemm0_done = reinterpret_cast<uint32_t*>(c->work + w_done);
+  p.ticket = reinterpret_cast<uint32_t*>(c->work + w_ctl);
+  p.done_ctas = reinterpret_cast<uint32_t*>(c->work + w_ctl + 64);
+  p.abort_word = reinterpret_cast<uint32_t*>(c->work + w_ctl + 128);
+  p.epoch = reinterpret_cast<uint64_t*>(c->work + w_ctl + 192);
+  p.status = reinterpret_cast<fmoe_status*>(c->work + w_status);
+  p.table = reinterpret_cast<const TokenSlot*>(c->work + w_table);
+  p.routes = reinterpret_cast<const Route*>(c->work + w_routes);
+
+  rc = make_map(&c->maps[0], p.ab_format, c->symm + L.landing, g.landing_rows, H);
+  if (rc == FMOE_OK) rc = make_map(&c->maps[1], p.ab_format, p.y, g.landing_rows, I);
+  if (rc != FMOE_OK) { free_ctx(c); return rc; }
+  c->committed = (W == 1);
+  if (W == 1) c->params.peers[0] = c->symm;
+  *out = c;
+  return FMOE_OK;
+}
+
+int fmoe_symm_bytes(const fmoe_ctx* ctx, size_t* bytes) {
+  if (ctx == nullptr || bytes == nullptr) return set_error(FMOE_ERR_INVALID_ARG, "null argument");
+  *bytes = ctx->lay.total;
+  return FMOE_OK;
+}
+
+int fmoe_symm_export(fmoe_ctx* ctx, void* handle_out) {
+  if (ctx == nullptr || handle_out == nullptr) return set_error(FMOE_ERR_INVALID_ARG, "null argument");
+  static_assert(sizeof(cudaIpcMemHandle_t) == FMOE_IPC_HANDLE_BYTES, "IPC handle size");
+  FMOE_CUDA(cudaSetDevice(ctx->device));
+  cudaIpcMemHandle_t h;
+  FMOE_CUDA(cudaIpcGetMemHandle(&h, ctx->symm));
+  std::memcpy(handle_out, &h, sizeof(h));
+  return FMOE_OK;
+}
+
+int fmoe_symm_import(fmoe_ctx* ctx, int32_t peer, const void* handle) {
+  if (ctx == nullptr || handle == nullptr) return set_error(FMOE_ERR_INVALID_ARG, "null argument");
+  if (peer < 0 || peer >= ctx->W) return set_error(FMOE_ERR_INVALID_ARG, "peer rank out of range");
+  if (peer == ctx->rank) return FMOE_OK;
+  FMOE_CUDA(cudaSetDevice(ctx->device));
+  cudaIpcMemHandle_t h;
+  std::memcpy(&h, handle, sizeof(h));
+  void* base = nullptr;
+  FMOE_CUDA(cudaIpcOpenMemHandle(&base, h, cudaIpcMemLazyEnablePeerAccess));
+  ctx->peers[peer] = static_cast<char*>(base);
+  ctx->imported[peer] = true;
+  return FMOE_OK;
+}
+
+int fmoe_symm_base(fmoe_ctx* ctx, void** base_out) {
+  if (ctx == nullptr || base_out == nullptr) return set_error(FMOE_ERR_INVALID_ARG, "null argument");
+  *base_out = ctx->symm;
+  return FMOE_OK;
+}
+
+int fmoe_symm_set_peer(fmoe_ctx* ctx, int32_t peer, void* peer_base) {
+  if (ctx == nullptr || peer_base == nullptr) return set_error(FMOE_ERR_INVALID_ARG, "null argument");
+  if (peer < 0 || peer >= ctx->W) return set_error(FMOE_ERR_INVALID_ARG, "peer rank out of range");
+  if (peer != ctx->rank) ctx->peers[peer] = static_cast<char*>(peer_base);
+  return FMOE_OK;
+}
+
+int fmoe_ctx_commit(fmoe_ctx* ctx) {
+  if (ctx == nullptr) return set_error(FMOE_ERR_INVALID_ARG, "null context");
+  for (int r = 0; r < ctx->W; ++r) {
+    if (ctx->peers[r] == nullptr)
+      return set_error(FMOE_ERR_NOT_READY, "symmetric block of ep rank " + std::to_string(r) + " has not been imported");
+    ctx->params.peers[r] = ctx->peers[r];
+  }
+  ctx->committed = true;
+  return FMOE_OK;
+}
+
+int fmoe_token_indices(fmoe_ctx* ctx, void** table_out) {
+  if (ctx == nullptr || table_out == nullptr) return set_error(FMOE_ERR_INVALID_ARG, "null argument");
+  *table_out = const_cast<TokenSlot*>(ctx->params.table);
+  return FMOE_OK;
+}
+
+int fmoe_get_geometry(const fmoe_ctx* ctx, fmoe_geometry* out) {
+  if (ctx == nullptr || out == nullptr) return set_error(FMOE_ERR_INVALID_ARG, "null argument");
+  *out = ctx->geo;
+  return FMOE_OK;
+}
+
+int fmoe_debug_buffer(fmoe_ctx* ctx, int32_t which, void** ptr_out, size_t* bytes_out) {
+  if (ctx == nullptr || ptr_out == nullptr || bytes_out == nullptr)
+    return set_error(FMOE_ERR_INVALID_ARG, "null argument");
+  const MoeParams& p = ctx->params;
+  switch (which) {
+    case 0: *ptr_out = ctx->symm + ctx->lay.landing; *bytes_out = static_cast<size_t>(p.landing_rows) * p.H * 2; break;
+    case 1: *ptr_out = ctx->symm + ctx->lay.landing_meta; *bytes_out = sizeof(uint32_t) * p.landing_rows; break;
+    case 2: *ptr_out = p.y; *bytes_out = static_cast<size_t>(p.landing_rows) * p.I * 2; break;
+    case 3: *ptr_out = ctx->symm + ctx->lay.ret; *bytes_out = static_cast<size_t>(p.S) * p.k * p.H * 2; break;
+    case 4: *ptr_out = const_cast<Route*>(p.routes); *bytes_out = sizeof(Route) * p.S * p.k; break;
+    default: return set_error(FMOE_ERR_INVALID_ARG, "unknown buffer id");
+  }
+  return FMOE_OK;
+}
+
+int fmoe_ctx_destroy(fmoe_ctx* ctx, void* stream) {
+  if (ctx == nullptr) return FMOE_OK;
+  cudaSetDevice(ctx->device);
+  cudaStreamSynchronize(static_cast<cudaStream_t>(stream));
+  free_ctx(ctx);
+  return FMOE_OK;
+}
+
+int fmoe_forward(fmoe_ctx* ctx, const fmoe_forward_args* a, void* stream) {
+  if (ctx == nullptr || a == nullptr) return set_error(FMOE_ERR_INVALID_ARG, "null argument");
+  if (!ctx->committed) return set_error(FMOE_ERR_NOT_READY, "call fmoe_ctx_commit after importing every peer");
+  const bool gated = ctx->params.gated != 0;
+  if (a->tokens == nullptr || a->expert_counts == nullptr || a->local_expert_up == nullptr ||
+      a->local_expert_down == nullptr || a->moe_out == nullptr || (gated && a->local_expert_up_v == nullptr))
+    return set_error(FMOE_ERR_INVALID_ARG, "a required device pointer is null");
+  if ((reinterpret_cast<uintptr_t>(a->tokens) | reinterpret_cast<uintptr_t>(a->moe_out) |
+       reinterpret_cast<uintptr_t>(a->local_expert_up) | reinterpret_cast<uintptr_t>(a->local_expert_up_v) |
+       reinterpret_cast<uintptr_t>(a->local_expert_down)) & 15)
+    return set_error(FMOE_ERR_INVALID_ARG, "tokens, moe_out and the expert weights must be 16-byte aligned");
+  MoeParams p = ctx->params;
+  const void* up_v = gated ? a->local_expert_up_v : a->local_expert_up;
+  if (ctx->map_src[0] != a->local_expert_up || ctx->map_src[1] != up_v || ctx->map_src[2] != a->local_expert_down) {
+    int rc = make_map(&ctx->maps[2], p.ab_format, a->local_expert_up, static_cast<uint64_t>(p.nLx) * p.I, p.H);
+    if (rc == FMOE_OK) rc = make_map(&ctx->maps[3], p.ab_format, up_v, static_cast<uint64_t>(p.nLx) * p.I, p.H);
+    if (rc == FMOE_OK) rc = make_map(&ctx->maps[4], p.ab_format, a->local_expert_down, static_cast<uint64_t>(p.nLx) * p.H, p.I);
+    if (rc != FMOE_OK) return rc;
+    ctx->map_src[0] = a->local_expert_up; ctx->map_src[1] = up_v; ctx->map_src[2] = a->local_expert_down;
+  }
+  p.tokens = a->tokens; p.expert_counts = a->expert_counts;
+  p.bias_up = a->local_bias_up; p.bias_up_v = a->local_bias_up_v; p.bias_down = a->local_bias_down;
+  p.out = a->moe_out; p.alpha = a->swish_alpha; p.beta = a->swish_beta;
+  FMOE_CUDA(launch_moe(p, ctx->maps, ctx->geo.grid, ctx->geo.smem_bytes, static_cast<cudaStream_t>(stream)));
+  return FMOE_OK;
+}
+
+int fmoe_last_status(fmoe_ctx* ctx, void* stream, fmoe_status* out) {
+  if (ctx == nullptr || out == nullptr) return set_error(FMOE_ERR_INVALID_ARG, "null argument");
+  FMOE_CUDA(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)));
+  FMOE_CUDA(cudaMemcpy(out, ctx->params.status, sizeof(fmoe_status), cudaMemcpyDeviceToHost));
+  return out->code;
+}
+
+int fmoe_router_create(const fmoe_model_desc* model, int32_t device_id, int32_t return_logits, void* stream,
+                       fmoe_router** out) {
+  if (out == nullptr) return set_error(FMOE_ERR_INVALID_ARG, "out is null");
+  *out = nullptr;
+  int rc = validate_model(model);
+  if (rc != FMOE_OK) return rc;
+  if (model->data_type == FMOE_DT_FP64) return set_error(FMOE_ERR_UNSUPPORTED, "the router handles BF16, FP16 and FP32");
+  if (model->token_dim % 8 != 0) return set_error(FMOE_ERR_INVALID_ARG, "token_dim must be a multiple of 8");
+  if (static_cast<size_t>(model->num_experts) * 4 * 8 * 4 > 200 * 1024)
+    return set_error(FMOE_ERR_UNSUPPORTED, "num_experts too large for the router's shared-memory rows");
+  fmoe_router* r = new (std::nothrow) fmoe_router();
+  if (r == nullptr) return set_error(FMOE_ERR_NO_MEMORY, "host allocation failed");
+  r->model = *model; r->device = device_id; r->return_logits = return_logits;
+  cudaError_t ce = cudaSetDevice(device_id);
+  const size_t n = static_cast<size_t>(model->tokens_per_rank) * model->top_k;
+  if (ce == cudaSuccess) ce = cudaMalloc(&r->topk_idx, n * sizeof(int32_t));
+  if (ce == cudaSuccess) ce = cudaMalloc(&r->topk_w, n * sizeof(float));
+  if (ce != cudaSuccess) {
+    if (r->topk_idx) cudaFree(r->topk_idx);
+    delete r;
+    return set_error(FMOE_ERR_CUDA, std::string("router scratch: ") + cudaGetErrorString(ce));
+  }
+  (void)stream;
+  *out = r;
+  return FMOE_OK;
+}
+
+int fmoe_router_forward(fmoe_router* router, fmoe_ctx* moe, const fmoe_router_args* a, void* stream) {
+  if (router == nullptr || moe == nullptr || a == nullptr) return set_error(FMOE_ERR_INVALID_ARG, "null argument");
+  if (a->tokens == nullptr || a->weights == nullptr || a->expert_counts == nullptr)
+    return set_error(FMOE_ERR_INVALID_ARG, "tokens, weights and expert_counts are required");
+  if (router->return_logits && a->routing == nullptr)
+    return set_error(FMOE_ERR_INVALID_ARG, "this router was created with return_logits: routing is required");
+  if ((reinterpret_cast<uintptr_t>(a->tokens) | reinterpret_cast<uintptr_t>(a->weights)) & 15)
+    return set_error(FMOE_ERR_INVALID_ARG, "tokens and weights must be 16-byte aligned");
+  const fmoe_model_desc& m = router->model;
+  const fmoe_model_desc& mm = moe->model;
+  if (m.tokens_per_rank != mm.tokens_per_rank || m.num_experts != mm.num_experts || m.top_k != mm.top_k ||
+      m.expert_peer_capacity != mm.expert_peer_capacity || m.token_dim != mm.token_dim)
+    return set_error(FMOE_ERR_INVALID_ARG, "router and MoE context describe different layers");
+  RouterParams p{};
+  p.S = m.tokens_per_rank; p.H = m.token_dim; p.E = m.num_experts; p.k = m.top_k;
+  p.EC = m.expert_peer_capacity; p.round_ec = moe->geo.round_ec; p.dtype = m.data_type;
+  p.tokens = a->tokens; p.weights = a->weights; p.logit_bias = a->logit_bias;
+  p.routing = router->return_logits ? a->routing : nullptr;
+  p.topk_idx = router->topk_idx; p.topk_w = router->topk_w;
+  p.expert_counts = a->expert_counts;
+  p.table = const_cast<TokenSlot*>(moe->params.table);
+  p.routes = const_cast<Route*>(moe->params.routes);
+  FMOE_CUDA(launch_router(p, static_cast<cudaStream_t>(stream)));
+  return FMOE_OK;
+}
+
+int fmoe_router_destroy(fmoe_router* router, void* stream) {
+  if (router == nullptr) return FMOE_OK;
+  cudaSetDevice(router->device);
+  cudaStreamSynchronize(static_cast<cudaStream_t>(stream));
+  cudaFree(router->topk_idx);
+  cudaFree(router->topk_w);
+  delete router;
+  return FMOE_OK;
+}
+
+int fmoe_forward_host(fmoe_ctx* ctx, fmoe_router* router, const void* tokens_host, void* out_host,
+                      const fmoe_router_args* rargs, const fmoe_forward_args* args, void* stream) {
+  if (ctx == nullptr || router == nullptr || tokens_host == nullptr || out_host == nullptr ||
+      rargs == nullptr || args == nullptr)
+    return set_error(FMOE_ERR_INVALID_ARG, "null argument");
+  const size_t bytes = static_cast<size_t>(ctx->params.S) * ctx->params.H * 2;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (ctx->stage_tokens == nullptr) {
+    FMOE_CUDA(cudaSetDevice(ctx->device));
+    FMOE_CUDA(cudaMalloc(&ctx->stage_tokens, bytes));
+    FMOE_CUDA(cudaMalloc(&ctx->stage_out, bytes));
+  }
+  FMOE_CUDA(cudaMemcpyAsync(ctx->stage_tokens, tokens_host, bytes, cudaMemcpyHostToDevice, st));
+  fmoe_router_args ra = *rargs;
+  ra.tokens = ctx->stage_tokens;
+  int rc = fmoe_router_forward(router, ctx, &ra, stream);
+  if (rc != FMOE_OK) return rc;
+  fmoe_forward_args fa = *args;
+  fa.tokens = ctx->stage_tokens;
+  fa.moe_out = ctx->stage_out;
+  rc = fmoe_forward(ctx, &fa, stream);
+  if (rc != FMOE_OK) return rc;
+  FMOE_CUDA(cudaMemcpyAsync(out_host, ctx->stage_out, bytes, cudaMemcpyDeviceToHost, st));
+  FMOE_CUDA(cudaStreamSynchronize(st));
+  return FMOE_OK;
+}
+
+}  // extern "C"

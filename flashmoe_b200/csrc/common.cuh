@@ -1,0 +1,112 @@
+// Structures shared by the host code and the kernels.
+#pragma once
+#include <cstddef>
+#include <cstdint>
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include "../../include/flashmoe_b200.h"
+
+namespace fmoe {
+
+// One routing-table entry, the reference's TPS (csrc/include/flashmoe/infra/packed.cuh:8-11).
+struct __align__(8) TokenSlot {
+  uint32_t token;
+  float weight;
+};
+
+// Per (token, choice) record the router leaves for the combine step: which expert, which slot
+// of that expert's routing-table row (slot >= EC means the pair was dropped), which weight.
+struct __align__(16) Route {
+  int32_t expert;
+  int32_t slot;
+  float weight;
+  int32_t pad;
+};
+
+constexpr int kTileM = 128;      // rows of an expert's batch per tile (UMMA M)
+constexpr int kTileK = 64;       // 64 x 16-bit = one 128-byte swizzle span
+constexpr int kUmmaN = 256;      // UMMA N: gate|up halves for GEMM0, 256 output columns for GEMM1
+constexpr int kStages = 4;       // TMA -> UMMA ring depth
+constexpr int kAccBufs = 2;      // TMEM accumulator double buffer (2 x 256 columns)
+constexpr int kTaskSlots = 4;    // task ring between the scheduler warp and its consumers
+constexpr int kThreads = 192;    // warp 0 scheduler + TMA, warp 1 UMMA, warps 2..5 epilogue
+constexpr uint32_t kStageABytes = kTileM * kTileK * 2;
+constexpr uint32_t kStageBBytes = kUmmaN * kTileK * 2;
+constexpr uint32_t kStageBytes = kStageABytes + kStageBBytes;
+
+constexpr uint32_t kMetaSrcShift = 26;  // landing meta = (source rank << 26) | return row
+
+// Offsets inside a rank's symmetric block (identical on every rank).
+struct SymmLayout {
+  size_t cnt_table;     // int32  [2][W][E]   counts every rank published, by epoch parity
+  size_t cnt_flag;      // uint64 [2][W]      epoch number that table holds
+  size_t disp_arrived;  // uint32 [W][nLx]    rows landed from (source rank, local expert)
+  size_t ret_arrived;   // uint32 [1]         (rows x N1 tiles) returned to this rank
+  size_t landing;       // Element [landing_rows][H]  dispatched rows, packed per local expert
+  size_t landing_meta;  // uint32 [landing_rows]
+  size_t ret;           // Element [S*k][H]   expert outputs for this rank's (token, choice) pairs
+  size_t total;
+};
+
+// Everything the persistent kernel needs; passed by value as a __grid_constant__.
+struct MoeParams {
+  int S, H, I, E, k, EC, round_ec;
+  int W, rank, nLx;
+  int gated, act, ab_format;  // ab_format: 0 fp16, 1 bf16
+  int tiles_n0, tiles_n1;
+  int landing_rows;
+  int max_mtiles;
+  float alpha, beta;
+
+  const int32_t* owner;    // [E] expert -> ep rank
+  const int32_t* lidx;     // [E] expert -> index among its owner's experts
+  const int32_t* local_e;  // [W][nLx] -> global expert id
+
+  char* peers[FMOE_MAX_WORLD];  // symmetric block of every rank (peers[rank] = own)
+  SymmLayout lay;
+
+  // private workspace
+  void* y;                 // Element [landing_rows][I]  GEMM0 output
+  uint32_t* gemm0_done;    // [max_mtiles] finished N0 tiles per M tile
+  uint32_t* ticket;        // next task
+  uint32_t* done_ctas;
+  uint64_t* epoch;         // forward number, bumped by the last CTA to leave
+  uint32_t* abort_word;
+  fmoe_status* status;
+
+  const TokenSlot* table;  // [E][round_ec]
+  const Route* routes;     // [S][k]
+
+  // per forward
+  const void* tokens;
+  const int32_t* expert_counts;
+  const void* bias_up;
+  const void* bias_up_v;
+  const void* bias_down;
+  void* out;
+};
+
+struct RouterParams {
+  int S, H, E, k, EC, round_ec;
+  int dtype;                // FMOE_DT_*
+  const void* tokens;
+  const void* weights;
+  const float* logit_bias;
+  float* routing;           // [S, E] or null
+  int32_t* topk_idx;        // [S, k] scratch
+  float* topk_w;            // [S, k] scratch
+  int32_t* expert_counts;   // [E]
+  TokenSlot* table;         // [E][round_ec]
+  Route* routes;            // [S][k]
+};
+
+cudaError_t launch_router(const RouterParams& p, cudaStream_t stream);
+size_t moe_smem_bytes(int W, int E, int nLx);
+cudaError_t moe_prepare_kernel(size_t smem);
+cudaError_t launch_moe(const MoeParams& p, const CUtensorMap* maps, int grid, size_t smem,
+                       cudaStream_t stream);
+
+extern unsigned long long g_launches;
+
+}  // namespace fmoe

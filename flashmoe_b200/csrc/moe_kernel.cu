@@ -1,0 +1,713 @@
+// The MoE-layer forward as one persistent sm_100a kernel: count exchange, dispatch, expert
+// GEMMs (tcgen05 / TMEM, TMA-fed), return of the expert outputs, combine.
+//
+// It replaces the reference's moe::forward kernel and its in-kernel runtime
+// (csrc/include/flashmoe/moe.cuh:161-247, os.cuh, scheduler.cuh, subscriber.cuh,
+// dispatch.cuh, processor.cuh, combine.cuh).  What is kept is the contract: one launch per
+// forward, experts sharded over the ranks of one NVLink box, tokens pushed to the expert's
+// owner by in-kernel peer stores, results pushed back, readiness carried by flags and
+// counters in a symmetric block, nothing cleared by the host between launches.  What is
+// different, and why:
+//
+//  * Rows are PACKED per expert at the owner (all source ranks back to back), so M tiles are
+//    full whenever an expert has >= 128 rows in total; the reference tiles per (source rank,
+//    expert) and pads each to the tile height (subscriber.cuh:121-160).  Packing needs every
+//    rank's per-expert counts first: each launch opens with a count exchange through the
+//    symmetric block (W*E ints per rank), which doubles as the epoch handshake.
+//  * No central "OS" CTA: every CTA runs the same scheduler warp, which takes tickets from one
+//    global counter over a fixed task order (GEMM0 of expert i, then GEMM1 of expert i-1)
+//    and waits on the task's readiness counters itself.  Tickets are handed out in an order
+//    in which a task only ever waits on tasks with smaller tickets, so the kernel cannot
+//    deadlock as long as all CTAs are co-resident (grid <= SM count, one CTA per SM).
+//  * Each CTA is warp-specialised: warp 0 = scheduler + TMA producer, warp 1 = UMMA issuer
+//    and TMEM owner, warps 2..5 = epilogue.  A 4-stage TMA->UMMA ring (48 KB per stage) and
+//    a double-buffered 2 x 256-column TMEM accumulator overlap loads, MMA and epilogue.
+//  * Gate and up projections are ONE UMMA of N = 256 (gate rows | up rows in the B tile);
+//    the SiLU-gate product is formed in the epilogue straight from TMEM.  The reference
+//    runs its main loop twice and parks the gate tile in shared memory
+//    (processor.cuh:97-136).  Rounding points are the reference's: the activated gate value
+//    is rounded to Element, the product is rounded to Element, the GEMM1 output is rounded
+//    to Element.
+//  * Expert outputs return to the token's owner as rows indexed by (token, choice); the owner
+//    sums a token's k rows in fp32 in selection order and rounds once (the reference
+//    accumulates with Element-precision atomics in arrival order, combine.cuh:120-223).
+//
+// Every wait is bounded; a wait that runs out records where in `status`, raises the
+// kernel-wide abort word and every role leaves through the common exit (TMEM freed).
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include "common.cuh"
+#include "ptx.cuh"
+
+namespace fmoe {
+
+unsigned long long g_launches = 0;
+
+namespace {
+
+using namespace ptx;
+
+struct alignas(64) TmaMaps {
+  CUtensorMap landing;  // [landing_rows, H]   box 64 x 128
+  CUtensorMap y;        // [landing_rows, I]   box 64 x 128
+  CUtensorMap up;       // [nLx*I, H]          box 64 x 128
+  CUtensorMap up_v;     // [nLx*I, H]          box 64 x 128
+  CUtensorMap down;     // [nLx*H, I]          box 64 x 128
+};
+
+enum : int { kTaskGemm0 = 0, kTaskGemm1 = 1, kTaskStop = 2 };
+
+struct Task {
+  int kind, lx, mt, row0, rows, n, m_in_expert, pad;
+};
+
+struct Control {
+  uint64_t full[kStages], empty[kStages];
+  uint64_t acc_full[kAccBufs], acc_empty[kAccBufs];
+  uint64_t task_full[kTaskSlots], task_empty[kTaskSlots];
+  Task tasks[kTaskSlots];
+  uint32_t tmem_base;
+  uint32_t ok;            // cleared when a CTA-wide wait failed
+  int total_tasks, n_segs, send_rows, expected_ret;
+  uint64_t epoch;
+};
+
+__device__ __forceinline__ void fail(const MoeParams& p, int phase, long long detail) {
+  if (atomicCAS(p.abort_word, 0u, 1u) == 0u) {
+    p.status->code = FMOE_ERR_DEVICE_TIMEOUT;
+    p.status->phase = phase;
+    p.status->rank = p.rank;
+    p.status->cta = static_cast<int>(blockIdx.x);
+    p.status->detail = detail;
+    __threadfence_system();
+  }
+}
+
+// Spin until *ctr >= want (acquire, system scope).  false = gave up.
+__device__ __forceinline__ bool wait_counter_sys(const uint32_t* ctr, uint32_t want,
+                                                 const MoeParams& p) {
+  if (ld_acquire_sys(ctr) >= want) return true;
+  SpinGuard g;
+  while (ld_acquire_sys(ctr) < want) {
+    if (g.expired(p.abort_word)) return ld_acquire_sys(ctr) >= want;
+  }
+  return true;
+}
+__device__ __forceinline__ bool wait_counter_gpu(const uint32_t* ctr, uint32_t want,
+                                                 const MoeParams& p) {
+  if (ld_acquire_gpu(ctr) >= want) return true;
+  SpinGuard g;
+  while (ld_acquire_gpu(ctr) < want) {
+    if (g.expired(p.abort_word)) return ld_acquire_gpu(ctr) >= want;
+  }
+  return true;
+}
+
+template <typename T> struct Cvt;
+template <> struct Cvt<__nv_bfloat16> {
+  static constexpr int kFormat = 1;
+  __device__ __forceinline__ static float up(uint32_t bits16) { return __uint_as_float(bits16 << 16); }
+  __device__ __forceinline__ static uint32_t pack(float a, float b) {
+    const __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<const uint32_t*>(&v);
+  }
+  __device__ __forceinline__ static float round(float a) {
+    return __bfloat162float(__float2bfloat16_rn(a));
+  }
+};
+template <> struct Cvt<__half> {
+  static constexpr int kFormat = 0;
+  __device__ __forceinline__ static float up(uint32_t bits16) {
+    return __half2float(__ushort_as_half(static_cast<unsigned short>(bits16)));
+  }
+  __device__ __forceinline__ static uint32_t pack(float a, float b) {
+    const __half2 v = __floats2half2_rn(a, b);
+    return *reinterpret_cast<const uint32_t*>(&v);
+  }
+  __device__ __forceinline__ static float round(float a) { return __half2float(__float2half_rn(a)); }
+};
+
+__device__ __forceinline__ float activate(float x, int act) {
+  switch (act) {
+    case FMOE_ACT_SILU: return __fdividef(x, 1.0f + __expf(-x));
+    case FMOE_ACT_GELU: return 0.5f * x * (1.0f + erff(x * 0.70710678118654752f));
+    case FMOE_ACT_RELU: return fmaxf(x, 0.0f);
+    default: return x;
+  }
+}
+
+template <typename T>
+__device__ __forceinline__ float bias_at(const void* bias, size_t idx) {
+  if (bias == nullptr) return 0.0f;
+  return Cvt<T>::up(static_cast<uint32_t>(__ldg(static_cast<const unsigned short*>(bias) + idx)));
+}
+
+// Shared-memory tables built by every CTA from the exchanged counts.
+struct Tables {
+  int* n;          // [W][E] rows rank s sends to expert e (clamped to EC)
+  int* dst_row0;   // [E]    landing row at e's owner where THIS rank's rows for e start
+  int* send_pref;  // [E+1]  prefix of n[rank][*]
+  int* lx_base;    // [nLx]  landing row where local expert lx starts (multiple of 128)
+  int* lx_rows;    // [nLx]  rows of local expert lx, all sources
+  int* lx_mt0;     // [nLx+1] prefix of M tiles
+  int* seg_first;  // [2 nLx + 1] first ticket of each segment of the task order
+  int* seg_kind;   // [2 nLx]
+  int* seg_lx;     // [2 nLx]
+  int* tot;        // [E]    rows expert e receives from all sources
+};
+
+__host__ __device__ inline size_t tables_ints(int W, int E, int nLx) {
+  return static_cast<size_t>(W) * E + E + (E + 1) + nLx + nLx + (nLx + 1) + (2 * nLx + 1) +
+         2 * nLx + 2 * nLx + E;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kThreads, 1)
+moe_forward_kernel(const __grid_constant__ MoeParams p, const __grid_constant__ TmaMaps maps) {
+  extern __shared__ uint8_t smem_raw[];
+  // stage ring first, 1024-byte aligned (128-byte swizzle atoms)
+  uint8_t* stages = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                               ~static_cast<uintptr_t>(1023));
+  Control* ctl = reinterpret_cast<Control*>(stages + kStages * kStageBytes);
+  int* tab = reinterpret_cast<int*>(ctl + 1);
+  Tables tb;
+  {
+    int* q = tab;
+    tb.n = q; q += p.W * p.E;
+    tb.dst_row0 = q; q += p.E;
+    tb.send_pref = q; q += p.E + 1;
+    tb.lx_base = q; q += p.nLx;
+    tb.lx_rows = q; q += p.nLx;
+    tb.lx_mt0 = q; q += p.nLx + 1;
+    tb.seg_first = q; q += 2 * p.nLx + 1;
+    tb.seg_kind = q; q += 2 * p.nLx;
+    tb.seg_lx = q; q += 2 * p.nLx;
+    tb.tot = q;
+  }
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int W = p.W, E = p.E, nLx = p.nLx;
+  char* const self = p.peers[p.rank];
+  constexpr int EB = 2;  // bytes per element
+
+  // ---- set-up: barriers, TMEM, epoch ---------------------------------------------------
+  if (tid == 0) {
+    for (int i = 0; i < kStages; ++i) { mbar_init(&ctl->full[i], 1); mbar_init(&ctl->empty[i], 1); }
+    for (int i = 0; i < kAccBufs; ++i) { mbar_init(&ctl->acc_full[i], 1); mbar_init(&ctl->acc_empty[i], 4); }
+    for (int i = 0; i < kTaskSlots; ++i) { mbar_init(&ctl->task_full[i], 1); mbar_init(&ctl->task_empty[i], 5); }
+    ctl->ok = 1;
+    ctl->epoch = *p.epoch;
+    mbar_fence_init();
+    prefetch_tmap(&maps.landing); prefetch_tmap(&maps.y); prefetch_tmap(&maps.up);
+    prefetch_tmap(&maps.up_v); prefetch_tmap(&maps.down);
+  }
+  if (warp == 1) {
+    tmem_alloc(&ctl->tmem_base, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint64_t epoch = ctl->epoch;
+  const uint64_t flag_val = epoch + 1;
+  const int parity = static_cast<int>(epoch & 1);
+
+  // ---- count exchange (CTA 0 publishes; everyone waits) --------------------------------
+  if (blockIdx.x == 0) {
+    // Counters of the previous forward are reset here: nobody can touch them before this
+    // rank's counts are out, because every rank needs every rank's counts to proceed.
+    for (int i = tid; i < p.max_mtiles; i += kThreads) p.gemm0_done[i] = 0;
+    uint32_t* arrived = reinterpret_cast<uint32_t*>(self + p.lay.disp_arrived);
+    for (int i = tid; i < W * nLx; i += kThreads) arrived[i] = 0;
+    if (tid == 0) {
+      *reinterpret_cast<uint32_t*>(self + p.lay.ret_arrived) = 0;
+      *p.ticket = 0;
+    }
+    __syncthreads();
+    for (int i = tid; i < W * E; i += kThreads) {
+      const int r = i / E, e = i - r * E;
+      int32_t* t = reinterpret_cast<int32_t*>(p.peers[r] + p.lay.cnt_table);
+      t[(static_cast<size_t>(parity) * W + p.rank) * E + e] = p.expert_counts[e];
+    }
+    __threadfence_system();
+    __syncthreads();
+    if (tid < W) {
+      uint64_t* f = reinterpret_cast<uint64_t*>(p.peers[tid] + p.lay.cnt_flag);
+      fence_acq_rel_sys();
+      st_release_sys(f + parity * W + p.rank, flag_val);
+    }
+  }
+  if (tid < W) {
+    const uint64_t* f = reinterpret_cast<const uint64_t*>(self + p.lay.cnt_flag) + parity * W + tid;
+    SpinGuard g;
+    bool ok = true;
+    while (ld_acquire_sys(f) != flag_val) {
+      if (g.expired(p.abort_word)) { ok = (ld_acquire_sys(f) == flag_val); break; }
+    }
+    if (!ok) { fail(p, FMOE_PHASE_COUNTS, tid); ctl->ok = 0; }
+  }
+  __syncthreads();
+  if (ctl->ok) {
+    const int32_t* t = reinterpret_cast<const int32_t*>(self + p.lay.cnt_table) +
+                       static_cast<size_t>(parity) * W * E;
+    for (int i = tid; i < W * E; i += kThreads) {
+      const int v = __ldcg(t + i);
+      tb.n[i] = v < p.EC ? (v < 0 ? 0 : v) : p.EC;
+    }
+  }
+  __syncthreads();
+  if (ctl->ok) {
+    // per expert: rows from all sources, and rows from sources below this rank
+    for (int e = tid; e < E; e += kThreads) {
+      int tot = 0, before = 0;
+      for (int s = 0; s < W; ++s) {
+        if (s == p.rank) before = tot;
+        tot += tb.n[s * E + e];
+      }
+      tb.tot[e] = tot;
+      tb.dst_row0[e] = before;
+    }
+  }
+  __syncthreads();
+  if (ctl->ok && tid < W) {
+    // landing-row base of every expert at its owner: that owner's experts in local order,
+    // each rounded up to whole M tiles
+    const int r = tid;
+    int base = 0;
+    for (int lx = 0; lx < nLx; ++lx) {
+      const int e = p.local_e[r * nLx + lx];
+      const int tot = tb.tot[e];
+      tb.dst_row0[e] += base;
+      if (r == p.rank) { tb.lx_base[lx] = base; tb.lx_rows[lx] = tot; }
+      base += (tot + kTileM - 1) / kTileM * kTileM;
+    }
+  }
+  __syncthreads();
+  if (ctl->ok && tid == 0) {
+    int sp = 0;
+    for (int e = 0; e < E; ++e) { tb.send_pref[e] = sp; sp += tb.n[p.rank * E + e]; }
+    tb.send_pref[E] = sp;
+    ctl->send_rows = sp;
+    ctl->expected_ret = sp * p.tiles_n1;
+    int mt = 0;
+    for (int lx = 0; lx < nLx; ++lx) { tb.lx_mt0[lx] = mt; mt += (tb.lx_rows[lx] + kTileM - 1) / kTileM; }
+    tb.lx_mt0[nLx] = mt;
+    // task order: G0(0), G0(1), G1(0), G0(2), G1(1), ..., G1(nLx-1)
+    int ns = 0, first = 0;
+    for (int i = 0; i <= nLx; ++i) {
+      if (i < nLx) {
+        tb.seg_first[ns] = first; tb.seg_kind[ns] = kTaskGemm0; tb.seg_lx[ns] = i; ++ns;
+        first += (tb.lx_mt0[i + 1] - tb.lx_mt0[i]) * p.tiles_n0;
+      }
+      if (i >= 1) {
+        tb.seg_first[ns] = first; tb.seg_kind[ns] = kTaskGemm1; tb.seg_lx[ns] = i - 1; ++ns;
+        first += (tb.lx_mt0[i] - tb.lx_mt0[i - 1]) * p.tiles_n1;
+      }
+    }
+    tb.seg_first[ns] = first;
+    ctl->n_segs = ns;
+    ctl->total_tasks = first;
+  }
+  __syncthreads();
+
+  // ---- dispatch: push this rank's routed rows to the experts' owners --------------------
+  if (ctl->ok) {
+    const int G = gridDim.x * (kThreads / 32);
+    const int gw = blockIdx.x * (kThreads / 32) + warp;
+    const long long R = ctl->send_rows;
+    int q = static_cast<int>(R * gw / G);
+    const int q_end = static_cast<int>(R * (gw + 1) / G);
+    const int vecs = p.H * EB / 16;
+    const uint4* tok_base = static_cast<const uint4*>(p.tokens);
+    while (q < q_end) {
+      int lo = 0, hi = E;  // largest e with send_pref[e] <= q
+      while (hi - lo > 1) {
+        const int mid = (lo + hi) >> 1;
+        if (tb.send_pref[mid] <= q) lo = mid; else hi = mid;
+      }
+      const int e = lo;
+      const int run_end = min(q_end, tb.send_pref[e + 1]);
+      const int r = p.owner[e], lx = p.lidx[e];
+      char* peer = p.peers[r];
+      const int run_start = q;
+      for (; q < run_end; ++q) {
+        const int j = q - tb.send_pref[e];
+        const uint32_t token = p.table[static_cast<size_t>(e) * p.round_ec + j].token;
+        const int drow = tb.dst_row0[e] + j;
+        const uint4* src = tok_base + static_cast<size_t>(token) * vecs;
+        uint4* dst = reinterpret_cast<uint4*>(peer + p.lay.landing) + static_cast<size_t>(drow) * vecs;
+        for (int v = lane; v < vecs; v += 32) dst[v] = __ldg(src + v);
+        int choice = 0;
+        if (lane < p.k) choice = (p.routes[static_cast<size_t>(token) * p.k + lane].expert == e) ? 1 : 0;
+        const unsigned b = __ballot_sync(0xffffffffu, choice != 0);
+        if (lane == 0) {
+          const uint32_t c = b ? static_cast<uint32_t>(__ffs(b) - 1) : 0u;
+          reinterpret_cast<uint32_t*>(peer + p.lay.landing_meta)[drow] =
+              (static_cast<uint32_t>(p.rank) << kMetaSrcShift) | (token * p.k + c);
+        }
+      }
+      const int sent = run_end - run_start;
+      __threadfence_system();
+      __syncwarp();
+      if (lane == 0 && sent > 0)
+        red_add_release_sys(reinterpret_cast<uint32_t*>(peer + p.lay.disp_arrived) + p.rank * nLx + lx,
+                            static_cast<uint32_t>(sent));
+    }
+  }
+
+  // ---- expert GEMMs ---------------------------------------------------------------------
+  const int nk0 = p.H / kTileK, nk1 = p.I / kTileK;
+  if (ctl->ok && warp == 0) {
+    if (lane == 0) {
+      // scheduler + TMA producer
+      uint32_t fill = 0;  // stage fills issued so far
+      uint32_t tslot = 0;
+      bool ok = true;
+      for (uint32_t it = 0; ok; ++it, tslot = (tslot + 1) % kTaskSlots) {
+        const int ticket = static_cast<int>(atomicAdd(p.ticket, 1u));
+        Task t{};
+        if (ticket >= ctl->total_tasks) {
+          t.kind = kTaskStop;
+        } else {
+          int lo = 0, hi = ctl->n_segs;
+          while (hi - lo > 1) {
+            const int mid = (lo + hi) >> 1;
+            if (tb.seg_first[mid] <= ticket) lo = mid; else hi = mid;
+          }
+          const int lx = tb.seg_lx[lo];
+          const int idx = ticket - tb.seg_first[lo];
+          const int mts = tb.lx_mt0[lx + 1] - tb.lx_mt0[lx];
+          t.kind = tb.seg_kind[lo];
+          t.lx = lx;
+          t.n = idx / mts;
+          t.m_in_expert = idx - t.n * mts;
+          t.mt = tb.lx_mt0[lx] + t.m_in_expert;
+          t.row0 = tb.lx_base[lx] + t.m_in_expert * kTileM;
+          t.rows = min(kTileM, tb.lx_rows[lx] - t.m_in_expert * kTileM);
+        }
+        if (!mbar_wait(&ctl->task_empty[tslot], ((it / kTaskSlots) & 1) ^ 1, p.abort_word)) {
+          fail(p, FMOE_PHASE_TASK, ticket); ok = false; break;
+        }
+        ctl->tasks[tslot] = t;
+        mbar_arrive(&ctl->task_full[tslot]);
+        if (t.kind == kTaskStop) break;
+
+        // readiness
+        if (t.kind == kTaskGemm0) {
+          const int e = p.local_e[p.rank * nLx + t.lx];
+          const uint32_t* arrived = reinterpret_cast<const uint32_t*>(self + p.lay.disp_arrived);
+          const int lo_row = t.m_in_expert * kTileM, hi_row = lo_row + t.rows;
+          int off = 0;
+          for (int s = 0; s < W && ok; ++s) {
+            const int ns = tb.n[s * E + e];
+            if (ns > 0 && off < hi_row && off + ns > lo_row) {
+              if (!wait_counter_sys(arrived + s * nLx + t.lx, static_cast<uint32_t>(ns), p)) {
+                fail(p, FMOE_PHASE_DISPATCH_ARRIVAL, s); ok = false;
+              }
+            }
+            off += ns;
+          }
+        } else {
+          if (!wait_counter_gpu(p.gemm0_done + t.mt, static_cast<uint32_t>(4 * p.tiles_n0), p)) {
+            fail(p, FMOE_PHASE_GEMM0_DONE, t.mt); ok = false;
+          }
+        }
+        if (!ok) break;
+        fence_proxy_async();
+
+        const bool g0 = t.kind == kTaskGemm0;
+        const int nk = g0 ? nk0 : nk1;
+        const CUtensorMap* map_a = g0 ? &maps.landing : &maps.y;
+        const CUtensorMap* map_b0 = g0 ? &maps.up : &maps.down;
+        const CUtensorMap* map_b1 = g0 ? (p.gated ? &maps.up_v : &maps.up) : &maps.down;
+        int brow0, brow1;
+        if (g0) {
+          if (p.gated) { brow0 = t.lx * p.I + t.n * 128; brow1 = brow0; }
+          else { brow0 = t.lx * p.I + t.n * 256; brow1 = brow0 + 128; }
+        } else {
+          brow0 = t.lx * p.H + t.n * 256; brow1 = brow0 + 128;
+        }
+        for (int kb = 0; kb < nk; ++kb, ++fill) {
+          const uint32_t s = fill % kStages;
+          if (!mbar_wait(&ctl->empty[s], ((fill / kStages) & 1) ^ 1, p.abort_word)) {
+            fail(p, FMOE_PHASE_PIPE_EMPTY, ticket); ok = false; break;
+          }
+          uint8_t* sa = stages + s * kStageBytes;
+          uint8_t* sb = sa + kStageABytes;
+          mbar_expect_tx(&ctl->full[s], kStageBytes);
+          tma_load_2d(sa, map_a, &ctl->full[s], kb * kTileK, t.row0);
+          tma_load_2d(sb, map_b0, &ctl->full[s], kb * kTileK, brow0);
+          tma_load_2d(sb + kStageBBytes / 2, map_b1, &ctl->full[s], kb * kTileK, brow1);
+        }
+      }
+      if (!ok) {
+        // let the copies already in flight land before this CTA's shared memory goes away
+        const uint32_t first = fill > kStages ? fill - kStages : 0;
+        for (uint32_t f = first; f < fill; ++f)
+          mbar_wait(&ctl->full[f % kStages], (f / kStages) & 1, nullptr);
+      }
+    }
+  } else if (ctl->ok && warp == 1) {
+    if (lane == 0) {
+      const uint32_t idesc = umma_idesc_f16(Cvt<T>::kFormat, kTileM, kUmmaN);
+      uint32_t fill = 0, tslot = 0, acc_it = 0;
+      for (uint32_t it = 0;; ++it, tslot = (tslot + 1) % kTaskSlots) {
+        if (!mbar_wait(&ctl->task_full[tslot], (it / kTaskSlots) & 1, p.abort_word)) {
+          fail(p, FMOE_PHASE_TASK, -1); break;
+        }
+        const Task t = ctl->tasks[tslot];
+        mbar_arrive(&ctl->task_empty[tslot]);
+        if (t.kind == kTaskStop) break;
+        const int nk = t.kind == kTaskGemm0 ? nk0 : nk1;
+        const uint32_t buf = acc_it % kAccBufs;
+        if (!mbar_wait(&ctl->acc_empty[buf], ((acc_it / kAccBufs) & 1) ^ 1, p.abort_word)) {
+          fail(p, FMOE_PHASE_TMEM_EMPTY, t.mt); break;
+        }
+        tc_fence_after_sync();
+        const uint32_t d_tmem = ctl->tmem_base + buf * kUmmaN;
+        bool ok = true;
+        for (int kb = 0; kb < nk; ++kb, ++fill) {
+          const uint32_t s = fill % kStages;
+          if (!mbar_wait(&ctl->full[s], (fill / kStages) & 1, p.abort_word)) {
+            fail(p, FMOE_PHASE_PIPE_FULL, t.mt); ok = false; break;
+          }
+          tc_fence_after_sync();
+          const uint32_t a_addr = smem_u32(stages + s * kStageBytes);
+          const uint32_t b_addr = a_addr + kStageABytes;
+#pragma unroll
+          for (int k = 0; k < kTileK / 16; ++k) {
+            umma_f16(d_tmem, umma_desc_sw128(a_addr + k * 32), umma_desc_sw128(b_addr + k * 32),
+                     idesc, (kb > 0 || k > 0) ? 1u : 0u);
+          }
+          umma_commit(&ctl->empty[s]);
+        }
+        if (!ok) break;
+        umma_commit(&ctl->acc_full[buf]);
+        ++acc_it;
+      }
+    }
+  } else if (ctl->ok) {
+    // epilogue warps: TMEM lane quadrant = warp id mod 4
+    const int quad = warp & 3;
+    const int row_in_tile = quad * 32 + lane;
+    uint32_t tslot = 0, acc_it = 0;
+    for (uint32_t it = 0;; ++it, tslot = (tslot + 1) % kTaskSlots) {
+      if (!mbar_wait(&ctl->task_full[tslot], (it / kTaskSlots) & 1, p.abort_word)) {
+        fail(p, FMOE_PHASE_TASK, -2); break;
+      }
+      const Task t = ctl->tasks[tslot];
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&ctl->task_empty[tslot]);
+      if (t.kind == kTaskStop) break;
+      const uint32_t buf = acc_it % kAccBufs;
+      if (!mbar_wait(&ctl->acc_full[buf], (acc_it / kAccBufs) & 1, p.abort_word)) {
+        fail(p, FMOE_PHASE_TMEM_FULL, t.mt); break;
+      }
+      tc_fence_after_sync();
+      const uint32_t taddr = ctl->tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + buf * kUmmaN;
+      const bool valid = row_in_tile < t.rows;
+      const int row = t.row0 + row_in_tile;
+
+      if (t.kind == kTaskGemm0) {
+        uint4* yrow = reinterpret_cast<uint4*>(static_cast<char*>(p.y) + static_cast<size_t>(row) * p.I * EB);
+        if (p.gated) {
+          const int col_base = t.n * 128;
+#pragma unroll 1
+          for (int c = 0; c < 4; ++c) {
+            uint32_t g[32], u[32];
+            __syncwarp();
+            tmem_ld_32x32(taddr + c * 32, g);
+            tmem_ld_32x32(taddr + 128 + c * 32, u);
+            tmem_ld_wait();
+            const int col0 = col_base + c * 32;
+            if (valid && col0 < p.I) {
+              uint32_t packed[16];
+#pragma unroll
+              for (int i = 0; i < 32; i += 2) {
+                float y2[2];
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                  const size_t bi = static_cast<size_t>(t.lx) * p.I + col0 + i + h;
+                  const float gate = (__uint_as_float(g[i + h]) + bias_at<T>(p.bias_up, bi)) * p.beta;
+                  const float tt = Cvt<T>::round(p.alpha * activate(gate, p.act));
+                  const float v = __uint_as_float(u[i + h]) + bias_at<T>(p.bias_up_v, bi);
+                  y2[h] = v * tt;
+                }
+                packed[i >> 1] = Cvt<T>::pack(y2[0], y2[1]);
+              }
+              uint4* dst = yrow + (col0 * EB) / 16;
+#pragma unroll
+              for (int v = 0; v < 4; ++v)
+                dst[v] = make_uint4(packed[4 * v], packed[4 * v + 1], packed[4 * v + 2], packed[4 * v + 3]);
+            }
+          }
+        } else {
+          const int col_base = t.n * 256;
+#pragma unroll 1
+          for (int c = 0; c < 8; ++c) {
+            uint32_t a[32];
+            __syncwarp();
+            tmem_ld_32x32(taddr + c * 32, a);
+            tmem_ld_wait();
+            const int col0 = col_base + c * 32;
+            if (valid && col0 < p.I) {
+              uint32_t packed[16];
+#pragma unroll
+              for (int i = 0; i < 32; i += 2) {
+                const size_t bi = static_cast<size_t>(t.lx) * p.I + col0 + i;
+                const float y0 = activate(__uint_as_float(a[i]) + bias_at<T>(p.bias_up, bi), p.act);
+                const float y1 = activate(__uint_as_float(a[i + 1]) + bias_at<T>(p.bias_up, bi + 1), p.act);
+                packed[i >> 1] = Cvt<T>::pack(y0, y1);
+              }
+              uint4* dst = yrow + (col0 * EB) / 16;
+#pragma unroll
+              for (int v = 0; v < 4; ++v)
+                dst[v] = make_uint4(packed[4 * v], packed[4 * v + 1], packed[4 * v + 2], packed[4 * v + 3]);
+            }
+          }
+        }
+        tc_fence_before_sync();
+        __threadfence();
+        __syncwarp();
+        if (lane == 0) {
+          mbar_arrive(&ctl->acc_empty[buf]);
+          red_add_release_gpu(p.gemm0_done + t.mt, 1u);
+        }
+      } else {
+        uint32_t meta = 0;
+        if (valid) meta = __ldcg(reinterpret_cast<const uint32_t*>(self + p.lay.landing_meta) + row);
+        const int src = static_cast<int>(meta >> kMetaSrcShift);
+        const uint32_t ret_row = meta & ((1u << kMetaSrcShift) - 1);
+        uint4* orow = reinterpret_cast<uint4*>(p.peers[valid ? src : p.rank] + p.lay.ret +
+                                               static_cast<size_t>(ret_row) * p.H * EB);
+        const int col_base = t.n * 256;
+#pragma unroll 1
+        for (int c = 0; c < 8; ++c) {
+          uint32_t a[32];
+          __syncwarp();
+          tmem_ld_32x32(taddr + c * 32, a);
+          tmem_ld_wait();
+          const int col0 = col_base + c * 32;
+          if (valid && col0 < p.H) {
+            uint32_t packed[16];
+#pragma unroll
+            for (int i = 0; i < 32; i += 2) {
+              const size_t bi = static_cast<size_t>(t.lx) * p.H + col0 + i;
+              const float o0 = __uint_as_float(a[i]) + bias_at<T>(p.bias_down, bi);
+              const float o1 = __uint_as_float(a[i + 1]) + bias_at<T>(p.bias_down, bi + 1);
+              packed[i >> 1] = Cvt<T>::pack(o0, o1);
+            }
+            uint4* dst = orow + (col0 * EB) / 16;
+#pragma unroll
+            for (int v = 0; v < 4; ++v)
+              dst[v] = make_uint4(packed[4 * v], packed[4 * v + 1], packed[4 * v + 2], packed[4 * v + 3]);
+          }
+        }
+        tc_fence_before_sync();
+        __threadfence_system();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&ctl->acc_empty[buf]);
+        // tell every owner how many of its rows this warp just delivered
+        for (int s = 0; s < W; ++s) {
+          const unsigned b = __ballot_sync(0xffffffffu, valid && src == s);
+          if (lane == 0 && b != 0)
+            red_add_release_sys(reinterpret_cast<uint32_t*>(p.peers[s] + p.lay.ret_arrived),
+                                static_cast<uint32_t>(__popc(b)));
+        }
+      }
+      ++acc_it;
+    }
+  }
+
+  // ---- combine: this rank's tokens, fp32 sum over the k returned rows -------------------
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  if (tid == 0 && ctl->ok && *reinterpret_cast<volatile uint32_t*>(p.abort_word) == 0) {
+    const uint32_t* ra = reinterpret_cast<const uint32_t*>(self + p.lay.ret_arrived);
+    if (!wait_counter_sys(ra, static_cast<uint32_t>(ctl->expected_ret), p)) {
+      fail(p, FMOE_PHASE_RETURN_ARRIVAL, ctl->expected_ret);
+      ctl->ok = 0;
+    }
+  }
+  __syncthreads();
+  if (ctl->ok && *reinterpret_cast<volatile uint32_t*>(p.abort_word) == 0) {
+    const int G = gridDim.x * (kThreads / 32);
+    const int vecs = p.H * EB / 16;
+    const uint4* ret = reinterpret_cast<const uint4*>(self + p.lay.ret);
+    uint4* out = static_cast<uint4*>(p.out);
+    for (int tkn = blockIdx.x * (kThreads / 32) + warp; tkn < p.S; tkn += G) {
+      if (p.k == 1) {
+        const Route r = p.routes[tkn];
+        if (r.slot < p.EC) {
+          for (int v = lane; v < vecs; v += 32)
+            out[static_cast<size_t>(tkn) * vecs + v] = __ldcg(ret + static_cast<size_t>(tkn) * vecs + v);
+        }
+      } else {
+        for (int v = lane; v < vecs; v += 32) {
+          float acc[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) acc[i] = 0.0f;
+          for (int j = 0; j < p.k; ++j) {
+            const Route r = p.routes[static_cast<size_t>(tkn) * p.k + j];
+            if (r.slot >= p.EC) continue;
+            const uint4 x = __ldcg(ret + (static_cast<size_t>(tkn) * p.k + j) * vecs + v);
+            const uint32_t w4[4] = {x.x, x.y, x.z, x.w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              acc[2 * i] = __fadd_rn(acc[2 * i], __fmul_rn(Cvt<T>::up(w4[i] & 0xffffu), r.weight));
+              acc[2 * i + 1] = __fadd_rn(acc[2 * i + 1], __fmul_rn(Cvt<T>::up(w4[i] >> 16), r.weight));
+            }
+          }
+          out[static_cast<size_t>(tkn) * vecs + v] =
+              make_uint4(Cvt<T>::pack(acc[0], acc[1]), Cvt<T>::pack(acc[2], acc[3]),
+                         Cvt<T>::pack(acc[4], acc[5]), Cvt<T>::pack(acc[6], acc[7]));
+        }
+      }
+    }
+  }
+
+  // ---- leave ------------------------------------------------------------------------------
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(ctl->tmem_base, 512);
+  if (tid == 0) {
+    __threadfence();
+    const uint32_t prev = atomicAdd(p.done_ctas, 1u);
+    if (prev == gridDim.x - 1) {
+      *p.done_ctas = 0;
+      *p.epoch = epoch + 1;
+      p.status->epoch = epoch + 1;
+    }
+  }
+}
+
+}  // namespace
+
+size_t moe_smem_bytes(int W, int E, int nLx) {
+  return 1024 + static_cast<size_t>(kStages) * kStageBytes + sizeof(Control) +
+         tables_ints(W, E, nLx) * sizeof(int) + 64;
+}
+
+cudaError_t moe_prepare_kernel(size_t smem) {
+  cudaError_t e = cudaFuncSetAttribute(moe_forward_kernel<__nv_bfloat16>,
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       static_cast<int>(smem));
+  if (e != cudaSuccess) return e;
+  return cudaFuncSetAttribute(moe_forward_kernel<__half>,
+                              cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+}
+
+cudaError_t launch_moe(const MoeParams& p, const CUtensorMap* maps, int grid, size_t smem,
+                       cudaStream_t stream) {
+  TmaMaps m;
+  m.landing = maps[0]; m.y = maps[1]; m.up = maps[2]; m.up_v = maps[3]; m.down = maps[4];
+  if (p.ab_format == 1) {
+    moe_forward_kernel<__nv_bfloat16><<<grid, kThreads, smem, stream>>>(p, m);
+  } else {
+    moe_forward_kernel<__half><<<grid, kThreads, smem, stream>>>(p, m);
+  }
+  ++g_launches;
+  return cudaGetLastError();
+}
+
+}  // namespace fmoe

@@ -1,0 +1,288 @@
+// Router: logits = X * Wr^T, softmax over all experts, top-k, routing-table construction.
+//
+// Replaces the reference's fused gate kernel (csrc/include/flashmoe/gate.cuh:98-565) with two
+// SIMT kernels whose fp32 arithmetic is fixed operation by operation, so that a CPU
+// restatement performing the same operations in the same order reproduces expert ids,
+// counts, slots AND probabilities bit for bit:
+//
+//  * dot product: H is cut into vectors of 8 elements; lane (v mod 32) consumes vector v;
+//    a lane walks its vectors in ascending order and each vector in ascending element
+//    order with acc = acc + x*w (one FMA for 16-bit inputs, whose products are exact in
+//    fp32; a rounded multiply followed by a rounded add for fp32 inputs); the 32 lane
+//    sums are folded with an xor-butterfly, offsets 16, 8, 4, 2, 1.
+//  * softmax: p_j = det_exp(x_j - max) / d with IEEE division; d is summed with element j
+//    on lane (j mod 32), ascending j per lane, then the same butterfly.
+//  * top-k: k rounds of arg-max on the probabilities, larger value wins, equal values go
+//    to the lower expert id (the reference's strict '>' ascending scan, gate.cuh:505-522);
+//    combine weight = p / (sum of the selected p, added in selection order).
+//  * slots: expert e's routing-table row lists the tokens that chose e in ascending token
+//    order (a second kernel scans tokens in order; the reference orders by tile arrival).
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include "common.cuh"
+
+namespace fmoe {
+
+namespace {
+
+constexpr int kRouterWarps = 8;
+constexpr int kRouterThreads = kRouterWarps * 32;
+
+// 2^f on [-0.5, 0.5]: (ln 2)^k / k!, k = 0..7, rounded to fp32.
+__device__ __forceinline__ float det_exp(float x) {
+  float t = __fmul_rn(x, 0x1.715476p+0f);
+  t = fmaxf(t, -100.0f);
+  const float n = rintf(t);
+  const float f = __fsub_rn(t, n);
+  float p = 0x1.ffcbfcp-17f;
+  p = __fadd_rn(__fmul_rn(p, f), 0x1.430912p-13f);
+  p = __fadd_rn(__fmul_rn(p, f), 0x1.5d87fep-10f);
+  p = __fadd_rn(__fmul_rn(p, f), 0x1.3b2ab6p-7f);
+  p = __fadd_rn(__fmul_rn(p, f), 0x1.c6b08ep-5f);
+  p = __fadd_rn(__fmul_rn(p, f), 0x1.ebfbep-3f);
+  p = __fadd_rn(__fmul_rn(p, f), 0x1.62e43p-1f);
+  p = __fadd_rn(__fmul_rn(p, f), 1.0f);
+  const float scale = __int_as_float((static_cast<int>(n) + 127) << 23);
+  return __fmul_rn(p, scale);
+}
+
+__device__ __forceinline__ float butterfly_sum(float v) {
+#pragma unroll
+  for (int off = 16; off >= 1; off >>= 1) v = __fadd_rn(v, __shfl_xor_sync(0xffffffffu, v, off));
+  return v;
+}
+
+template <typename T>
+struct Vec8;  // loads 8 consecutive elements as fp32
+
+template <>
+struct Vec8<__nv_bfloat16> {
+  static constexpr bool kExactProducts = true;
+  __device__ __forceinline__ static void load(const void* p, float (&f)[8]) {
+    const uint4 u = __ldg(reinterpret_cast<const uint4*>(p));
+    const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      f[2 * i] = __uint_as_float(w[i] << 16);
+      f[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+    }
+  }
+};
+template <>
+struct Vec8<__half> {
+  static constexpr bool kExactProducts = true;
+  __device__ __forceinline__ static void load(const void* p, float (&f)[8]) {
+    const uint4 u = __ldg(reinterpret_cast<const uint4*>(p));
+    const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 v = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
+      f[2 * i] = v.x;
+      f[2 * i + 1] = v.y;
+    }
+  }
+};
+template <>
+struct Vec8<float> {
+  static constexpr bool kExactProducts = false;
+  __device__ __forceinline__ static void load(const void* p, float (&f)[8]) {
+    const float4 a = __ldg(reinterpret_cast<const float4*>(p));
+    const float4 b = __ldg(reinterpret_cast<const float4*>(p) + 1);
+    f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w;
+    f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
+  }
+};
+
+// One warp owns TT consecutive tokens and walks the experts in groups of EG.
+template <typename T, int TT, int EG>
+__global__ void __launch_bounds__(kRouterThreads)
+router_topk_kernel(const RouterParams p) {
+  extern __shared__ float s_row[];  // [warps][TT][E]: logits, then exp, then probabilities
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int t0 = (blockIdx.x * kRouterWarps + warp) * TT;
+  if (t0 >= p.S) return;
+  const int H = p.H, E = p.E;
+  const int nvec = H >> 3;
+  const T* __restrict__ X = static_cast<const T*>(p.tokens);
+  const T* __restrict__ Wr = static_cast<const T*>(p.weights);
+  float* rows = s_row + static_cast<size_t>(warp) * TT * E;
+
+  for (int eg = 0; eg < E; eg += EG) {
+    float acc[TT][EG];
+#pragma unroll
+    for (int t = 0; t < TT; ++t)
+#pragma unroll
+      for (int e = 0; e < EG; ++e) acc[t][e] = 0.0f;
+
+    for (int v = lane; v < nvec; v += 32) {
+      float xv[TT][8];
+#pragma unroll
+      for (int t = 0; t < TT; ++t) {
+        const int tok = min(t0 + t, p.S - 1);  // a ragged last group recomputes the last token
+        Vec8<T>::load(X + static_cast<size_t>(tok) * H + v * 8, xv[t]);
+      }
+#pragma unroll
+      for (int e = 0; e < EG; ++e) {
+        float wv[8];
+        Vec8<T>::load(Wr + static_cast<size_t>(eg + e) * H + v * 8, wv);
+#pragma unroll
+        for (int t = 0; t < TT; ++t) {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            if constexpr (Vec8<T>::kExactProducts) {
+              acc[t][e] = __fmaf_rn(xv[t][j], wv[j], acc[t][e]);
+            } else {
+              acc[t][e] = __fadd_rn(acc[t][e], __fmul_rn(xv[t][j], wv[j]));
+            }
+          }
+        }
+      }
+    }
+#pragma unroll
+    for (int t = 0; t < TT; ++t) {
+#pragma unroll
+      for (int e = 0; e < EG; ++e) {
+        const float s = butterfly_sum(acc[t][e]);
+        if (lane == ((eg + e) & 31)) {
+          const float b = p.logit_bias ? __ldg(p.logit_bias + eg + e) : 0.0f;
+          rows[t * E + eg + e] = p.logit_bias ? __fadd_rn(s, b) : s;
+        }
+      }
+    }
+  }
+  __syncwarp();
+
+  for (int t = 0; t < TT; ++t) {
+    const int tok = t0 + t;
+    if (tok >= p.S) break;
+    float* r = rows + t * E;
+    float m = -INFINITY;
+    for (int j = lane; j < E; j += 32) m = fmaxf(m, r[j]);
+#pragma unroll
+    for (int off = 16; off >= 1; off >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, off));
+    float d = 0.0f;
+    for (int j = lane; j < E; j += 32) {
+      const float ex = det_exp(__fsub_rn(r[j], m));
+      r[j] = ex;
+      d = __fadd_rn(d, ex);
+    }
+    d = butterfly_sum(d);
+    for (int j = lane; j < E; j += 32) {
+      const float pr = __fdiv_rn(r[j], d);
+      r[j] = pr;
+      if (p.routing) p.routing[static_cast<size_t>(tok) * E + j] = pr;
+    }
+    float wsum = 0.0f, my_p = 0.0f;
+    int my_idx = 0;
+    for (int round = 0; round < p.k; ++round) {
+      float bv = -INFINITY;
+      int bi = 0x7fffffff;
+      for (int j = lane; j < E; j += 32) {
+        const float v = r[j];
+        if (v > bv) { bv = v; bi = j; }
+      }
+#pragma unroll
+      for (int off = 16; off >= 1; off >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, bv, off);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, off);
+        if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+      }
+      if (bi == 0x7fffffff) bi = 0;  // nothing left to pick (k > E, or all NaN)
+      if (lane == (bi & 31)) r[bi] = -INFINITY;
+      wsum = __fadd_rn(wsum, bv);
+      if (lane == (round & 31)) { my_p = bv; my_idx = bi; }
+      __syncwarp();
+    }
+    if (lane < p.k) {
+      p.topk_idx[static_cast<size_t>(tok) * p.k + lane] = my_idx;
+      p.topk_w[static_cast<size_t>(tok) * p.k + lane] = __fdiv_rn(my_p, wsum);
+    }
+    __syncwarp();
+  }
+}
+
+// One CTA per expert walks the tokens in ascending order and hands out slots.
+__global__ void __launch_bounds__(1024) router_slots_kernel(const RouterParams p) {
+  __shared__ int warp_tot[32];
+  __shared__ int base_s;
+  const int e = blockIdx.x;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  if (threadIdx.x == 0) base_s = 0;
+  __syncthreads();
+  for (int c0 = 0; c0 < p.S; c0 += blockDim.x) {
+    const int t = c0 + threadIdx.x;
+    int hit = -1;
+    if (t < p.S) {
+      for (int j = 0; j < p.k; ++j)
+        if (p.topk_idx[static_cast<size_t>(t) * p.k + j] == e) { hit = j; break; }
+    }
+    const unsigned ballot = __ballot_sync(0xffffffffu, hit >= 0);
+    const int before = __popc(ballot & ((1u << lane) - 1));
+    if (lane == 0) warp_tot[warp] = __popc(ballot);
+    __syncthreads();
+    int warp_base = 0, total = 0;
+    for (int w = 0; w < nwarps; ++w) {
+      const int c = warp_tot[w];
+      if (w < warp) warp_base += c;
+      total += c;
+    }
+    const int base = base_s;
+    if (hit >= 0) {
+      const int slot = base + warp_base + before;
+      const float wt = p.topk_w[static_cast<size_t>(t) * p.k + hit];
+      if (slot < p.EC)
+        p.table[static_cast<size_t>(e) * p.round_ec + slot] = TokenSlot{static_cast<uint32_t>(t), wt};
+      p.routes[static_cast<size_t>(t) * p.k + hit] = Route{e, slot, wt, 0};
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) base_s = base + total;
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) p.expert_counts[e] = base_s;
+}
+
+template <typename T, int TT>
+cudaError_t launch_topk_eg(const RouterParams& p, cudaStream_t stream) {
+  const int ctas = (p.S + kRouterWarps * TT - 1) / (kRouterWarps * TT);
+  const size_t smem = static_cast<size_t>(kRouterWarps) * TT * p.E * sizeof(float);
+  auto go = [&](auto kern) -> cudaError_t {
+    if (smem > 48 * 1024) {
+      cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           static_cast<int>(smem));
+      if (e != cudaSuccess) return e;
+    }
+    kern<<<ctas, kRouterThreads, smem, stream>>>(p);
+    ++g_launches;
+    return cudaGetLastError();
+  };
+  if (p.E % 32 == 0) return go(router_topk_kernel<T, TT, 32>);
+  if (p.E % 16 == 0) return go(router_topk_kernel<T, TT, 16>);
+  return go(router_topk_kernel<T, TT, 8>);
+}
+
+template <typename T>
+cudaError_t launch_topk(const RouterParams& p, cudaStream_t stream) {
+  if (p.S >= 3072) return launch_topk_eg<T, 4>(p, stream);
+  if (p.S >= 1536) return launch_topk_eg<T, 2>(p, stream);
+  return launch_topk_eg<T, 1>(p, stream);
+}
+
+}  // namespace
+
+cudaError_t launch_router(const RouterParams& p, cudaStream_t stream) {
+  cudaError_t e;
+  switch (p.dtype) {
+    case FMOE_DT_BF16: e = launch_topk<__nv_bfloat16>(p, stream); break;
+    case FMOE_DT_FP16: e = launch_topk<__half>(p, stream); break;
+    case FMOE_DT_FP32: e = launch_topk<float>(p, stream); break;
+    default: return cudaErrorInvalidValue;
+  }
+  if (e != cudaSuccess) return e;
+  const int threads = p.S >= 1024 ? 1024 : (p.S >= 256 ? 256 : 64);
+  router_slots_kernel<<<p.E, threads, 0, stream>>>(p);
+  ++g_launches;
+  return cudaGetLastError();
+}
+
+}  // namespace fmoe

@@ -1,0 +1,194 @@
+/*
+ * flashmoe_b200 -- C ABI of the B200-native MoE-layer forward.
+ *
+ * One shared library (libflashmoe_b200.so) exports exactly these entry points.  Every
+ * pointer argument that is documented as "device" is a plain device address; nothing in
+ * this interface carries a framework type.  Every function returns an fmoe_status_code
+ * (0 = success); no entry point throws, exits or terminates the process.
+ *
+ * Each declaration names the reference interface it replaces (paths inside the
+ * hnts03-moreh/FlashMoE project).  In the reference those are the functions a JIT-built
+ * pybind11 module exports per model description (flashmoe/bindings.py:154-185, 300-315)
+ * on top of the C++ host API (csrc/include/flashmoe/bootstrap.cuh, moe.cuh).
+ */
+#ifndef FLASHMOE_B200_H
+#define FLASHMOE_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define FMOE_MAX_WORLD 8          /* ranks of one NVSwitch box */
+#define FMOE_IPC_HANDLE_BYTES 64  /* sizeof(cudaIpcMemHandle_t) */
+
+typedef struct fmoe_ctx fmoe_ctx;       /* replaces flashmoe::Context (context.cuh:16-52) */
+typedef struct fmoe_router fmoe_router; /* replaces flashmoe::GateContext (context.cuh:54-59) */
+
+typedef enum fmoe_status_code {
+  FMOE_OK = 0,
+  FMOE_ERR_INVALID_ARG = 1,    /* reference: std::invalid_argument / std::runtime_error */
+  FMOE_ERR_UNSUPPORTED = 2,    /* shape, dtype, arch or topology this build does not handle */
+  FMOE_ERR_CUDA = 3,           /* a CUDA runtime or driver call failed (reference: exit(1)) */
+  FMOE_ERR_NOT_READY = 4,      /* peers not imported / context not committed */
+  FMOE_ERR_DEVICE_TIMEOUT = 5, /* a bounded device-side wait ran out (reference: spins forever) */
+  FMOE_ERR_NO_MEMORY = 6
+} fmoe_status_code;
+
+/* enum values of flashmoe/jit.py:22-40 */
+enum { FMOE_TOPO_NVLINK_ONLY = 0, FMOE_TOPO_MIXED = 1 };
+enum { FMOE_MLP_GATED = 0, FMOE_MLP_VANILLA = 1 };
+enum { FMOE_DT_BF16 = 0, FMOE_DT_FP16 = 1, FMOE_DT_FP32 = 2, FMOE_DT_FP64 = 3 };
+enum { FMOE_ACT_IDENTITY = 0, FMOE_ACT_SILU = 1, FMOE_ACT_GELU = 2, FMOE_ACT_RELU = 3 };
+
+/* The compile-time constants of a reference module (flashmoe/bindings.py:34-46), at run time. */
+typedef struct fmoe_model_desc {
+  int32_t tokens_per_rank;      /* S */
+  int32_t token_dim;            /* H */
+  int32_t ffn_size;             /* I */
+  int32_t num_experts;          /* E */
+  int32_t top_k;                /* k */
+  int32_t expert_peer_capacity; /* EC: rows one rank may send to one expert */
+  int32_t data_type;            /* FMOE_DT_* */
+  int32_t mlp_type;             /* FMOE_MLP_* */
+  int32_t act_type;             /* FMOE_ACT_* */
+  int32_t gpu_arch;             /* compute capability * 100; only 1000 and 1030 accepted */
+} fmoe_model_desc;
+
+/* Arguments of moe_initialize (flashmoe/bindings.py:68-110). */
+typedef struct fmoe_ep_desc {
+  int32_t ep_world;
+  int32_t ep_rank;
+  int32_t my_pe;
+  int32_t device_id;
+  int32_t num_local_experts;
+  int32_t topology;           /* FMOE_TOPO_*; only NVLINK_ONLY is implemented */
+  const int32_t* expert_map;  /* host, [num_experts]: expert -> ep rank */
+  const int32_t* rank_map;    /* host, [ep_world]: ep rank -> global rank */
+} fmoe_ep_desc;
+
+/* Arguments of moe_forward (flashmoe/bindings.py:112-140); all pointers device. */
+typedef struct fmoe_forward_args {
+  const void* tokens;            /* [S, H] Element */
+  const int32_t* expert_counts;  /* [E], written by the router */
+  const void* local_expert_up;   /* [nLx, I, H] activated branch */
+  const void* local_expert_up_v; /* [nLx, I, H] linear branch; null for a plain MLP */
+  const void* local_bias_up;     /* [nLx, I]; null = zero bias */
+  const void* local_bias_up_v;   /* [nLx, I]; null = zero bias */
+  const void* local_expert_down; /* [nLx, H, I] */
+  const void* local_bias_down;   /* [nLx, H]; null = zero bias */
+  void* moe_out;                 /* [S, H] Element */
+  float swish_alpha;
+  float swish_beta;
+} fmoe_forward_args;
+
+/* Arguments of gate_forward (flashmoe/bindings.py:266-290); all pointers device. */
+typedef struct fmoe_router_args {
+  const void* tokens;      /* [S, H] Element */
+  const void* weights;     /* [E, H] Element */
+  float* routing;          /* [S, E] fp32 softmax probabilities, or null */
+  int32_t* expert_counts;  /* [E] out: tokens that chose each expert (not clamped) */
+  const float* logit_bias; /* [E] fp32 added to the logits, or null (not in the reference) */
+} fmoe_router_args;
+
+/* What a device-side wait recorded when it gave up (no counterpart: the reference traps). */
+typedef struct fmoe_status {
+  int32_t code;   /* fmoe_status_code */
+  int32_t phase;  /* which wait: see FMOE_PHASE_* */
+  int32_t rank;
+  int32_t cta;
+  int64_t detail; /* wait-specific: tile id, peer rank, ... */
+  uint64_t epoch; /* forward number on this context */
+} fmoe_status;
+enum {
+  FMOE_PHASE_NONE = 0, FMOE_PHASE_COUNTS = 1, FMOE_PHASE_DISPATCH_ARRIVAL = 2,
+  FMOE_PHASE_GEMM0_DONE = 3, FMOE_PHASE_RETURN_ARRIVAL = 4, FMOE_PHASE_PIPE_FULL = 5,
+  FMOE_PHASE_PIPE_EMPTY = 6, FMOE_PHASE_TMEM_FULL = 7, FMOE_PHASE_TMEM_EMPTY = 8,
+  FMOE_PHASE_TASK = 9
+};
+
+/* --- context life cycle -------------------------------------------------------------- */
+
+/* Replaces flashmoe::initialize (bootstrap.cuh:197-374) minus the peer exchange: validates
+ * the description, allocates this rank's symmetric block (token landing area, return area,
+ * count tables, arrival counters) and its private workspace.  `stream` is a cudaStream_t. */
+int fmoe_ctx_create(const fmoe_model_desc* model, const fmoe_ep_desc* ep, void* stream,
+                    fmoe_ctx** out);
+
+/* Replaces nvshmem_malloc + nvshmem_ptr (bootstrap.cuh:141-151, 239-249): the symmetric
+ * block is an ordinary device allocation shared through CUDA IPC.  Export this rank's
+ * handle, gather the handles by any host-side means, import every peer's, then commit.
+ * With ep_world == 1 only fmoe_ctx_commit is needed. */
+int fmoe_symm_bytes(const fmoe_ctx* ctx, size_t* bytes);
+int fmoe_symm_export(fmoe_ctx* ctx, void* handle_out /* FMOE_IPC_HANDLE_BYTES */);
+int fmoe_symm_import(fmoe_ctx* ctx, int32_t peer_ep_rank, const void* handle);
+/* Peers living in the same process (tests): hand over the peer's base address directly. */
+int fmoe_symm_base(fmoe_ctx* ctx, void** base_out);
+int fmoe_symm_set_peer(fmoe_ctx* ctx, int32_t peer_ep_rank, void* peer_base);
+int fmoe_ctx_commit(fmoe_ctx* ctx);
+
+/* Replaces get_tIdx (flashmoe/bindings.py:142-144): device address of the routing table
+ * [E, roundEC] of {uint32 token, float weight} the router fills. */
+int fmoe_token_indices(fmoe_ctx* ctx, void** table_out);
+
+/* Replaces flashmoe::finalize (bootstrap.cuh:450-474). */
+int fmoe_ctx_destroy(fmoe_ctx* ctx, void* stream);
+
+/* --- the hot path -------------------------------------------------------------------- */
+
+/* Replaces moe::forwardHost / moe_forward (moe.cuh:255-260; flashmoe/bindings.py:112-140):
+ * one launch of the persistent kernel (dispatch, expert GEMMs, combine) on `stream`.
+ * Every rank of the group must call it the same number of times. */
+int fmoe_forward(fmoe_ctx* ctx, const fmoe_forward_args* args, void* stream);
+
+/* Replaces initializeGate / gate_initialize (bootstrap.cuh:413-447; bindings.py:238-264). */
+int fmoe_router_create(const fmoe_model_desc* model, int32_t device_id, int32_t return_logits,
+                       void* stream, fmoe_router** out);
+/* Replaces gate::forwardKernel launch / gate_forward (gate.cuh:588-608; bindings.py:266-290).
+ * Writes expert_counts, the routing table of `moe` and `moe`'s per-token route records. */
+int fmoe_router_forward(fmoe_router* router, fmoe_ctx* moe, const fmoe_router_args* args,
+                        void* stream);
+/* Replaces finalizeGate / gate_finalize (bootstrap.cuh:434-447). */
+int fmoe_router_destroy(fmoe_router* router, void* stream);
+
+/* The call sequence of quickstart.py:150-153 with HOST buffers: copies `tokens_host`
+ * (pinned or pageable, [S, H] Element) to the device, runs router + forward, copies the
+ * [S, H] result to `out_host` and synchronises `stream`.  `args->tokens`, `args->moe_out`
+ * and `rargs->tokens` are ignored (internal staging buffers are used). */
+int fmoe_forward_host(fmoe_ctx* ctx, fmoe_router* router, const void* tokens_host,
+                      void* out_host, const fmoe_router_args* rargs,
+                      const fmoe_forward_args* args, void* stream);
+
+/* --- diagnostics --------------------------------------------------------------------- */
+
+/* Reads the record the last forward left (synchronises `stream` first). */
+int fmoe_last_status(fmoe_ctx* ctx, void* stream, fmoe_status* out);
+const char* fmoe_strerror(int code);
+/* Last host-side error message of the calling thread (empty string if none). */
+const char* fmoe_last_error(void);
+/* Number of kernels this library has launched in this process (all contexts). */
+uint64_t fmoe_launch_count(void);
+
+/* Geometry chosen at create time, for tests and benchmarks. */
+typedef struct fmoe_geometry {
+  int32_t tile_m, tile_n0, tile_n1, tile_k, stages;
+  int32_t round_ec;        /* row stride of the routing table */
+  int32_t landing_rows;    /* rows of the token landing area */
+  int32_t grid, threads;   /* launch shape of the persistent kernel */
+  int32_t smem_bytes;
+  int64_t symm_bytes, workspace_bytes;
+} fmoe_geometry;
+int fmoe_get_geometry(const fmoe_ctx* ctx, fmoe_geometry* out);
+
+/* Device addresses of internal buffers, for stage-by-stage parity tests.
+ * which: 0 landing rows [landing_rows, H], 1 landing meta [landing_rows] u32,
+ *        2 GEMM0 output [landing_rows, I], 3 return rows [S*k, H],
+ *        4 route records [S, k] of {int32 expert, int32 slot, float weight} */
+int fmoe_debug_buffer(fmoe_ctx* ctx, int32_t which, void** ptr_out, size_t* bytes_out);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FLASHMOE_B200_H */

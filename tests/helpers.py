@@ -1,0 +1,55 @@
+"""Shared helpers of the parity tests: oracle runs, golden loading, error measures."""
+import os
+import sys
+
+import numpy as np
+import torch
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+ROOT = os.path.dirname(HERE)
+for p in (ROOT, HERE):
+    if p not in sys.path:
+        sys.path.insert(0, p)
+
+from flashmoe_b200.workloads import make_tokens, make_weights  # noqa: E402
+from oracle import moe_oracle as O  # noqa: E402
+
+# Tolerances of the output comparison (max |a - b| / max |b|): the benchmark description asks for
+# 2e-2 in BF16 (we also hold FP16 to it) and 1e-5 in FP32.
+REL_TOL = {0: 2e-2, 1: 2e-2, 2: 1e-5}
+
+
+def golden(name):
+    return np.load(os.path.join(HERE, "golden", name + ".npz"))
+
+
+def oracle_weights(lw):
+    return O.ExpertWeights(lw.up, lw.up_v, lw.down, lw.bias_up, lw.bias_up_v, lw.bias_down)
+
+
+def oracle_route(w, x=None, router_w=None, lw=None):
+    lw = lw or make_weights(w)
+    x = make_tokens(w) if x is None else x
+    router_w = lw.router if router_w is None else router_w
+    bias = None if lw.logit_bias is None else lw.logit_bias.numpy()
+    return O.route(x.float().numpy(), router_w.float().numpy(), w.top_k, w.expert_peer_capacity,
+                   logit_bias=bias)
+
+
+def oracle_layer(w, x=None, lw=None, combine="fp32"):
+    lw = lw or make_weights(w)
+    x = make_tokens(w) if x is None else x
+    bias = None if lw.logit_bias is None else lw.logit_bias.numpy()
+    return O.layer_forward(x, lw.router, oracle_weights(lw), w.top_k, w.expert_peer_capacity,
+                           int(w.mlp_type), int(w.act_type), logit_bias=bias, combine=combine)
+
+
+def max_rel_err(a: torch.Tensor, b: torch.Tensor) -> float:
+    a, b = a.double().cpu(), b.double().cpu()
+    return float((a - b).abs().max() / b.abs().max().clamp_min(1e-30))
+
+
+def from_bits(bits: np.ndarray, dtype: torch.dtype) -> torch.Tensor:
+    if dtype == torch.float32:
+        return torch.from_numpy(bits.view(np.float32).copy())
+    return torch.from_numpy(bits.view(np.int16).copy()).view(dtype)

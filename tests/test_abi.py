@@ -1,0 +1,104 @@
+"""The shared library loads, exports every entry point the header declares, and rejects bad
+descriptions with a status code (no GPU is touched: validation comes before any CUDA call)."""
+import ctypes as C
+import os
+import re
+
+import pytest
+
+import flashmoe_b200 as flashmoe
+from flashmoe_b200 import _native as N
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def declared_symbols():
+    text = open(os.path.join(ROOT, "include", "flashmoe_b200.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(fmoe_[a-z_0-9]+)\s*\(", text)))
+
+
+def test_library_exports_every_declared_symbol():
+    lib = N.lib()
+    names = declared_symbols()
+    assert len(names) >= 20
+    for n in names:
+        assert hasattr(lib, n), n
+    assert set(names) == set(N.SIGNATURES)
+
+
+def test_strerror_and_launch_count():
+    lib = N.lib()
+    assert lib.fmoe_strerror(0) == b"success"
+    assert b"device-side" in lib.fmoe_strerror(5)
+    assert lib.fmoe_launch_count() == 0
+
+
+def _desc(**kw):
+    d = dict(tokens_per_rank=128, token_dim=256, ffn_size=256, num_experts=8, top_k=2,
+             expert_peer_capacity=128, data_type=0, mlp_type=0, act_type=1, gpu_arch=1000)
+    d.update(kw)
+    return N.ModelDesc(*[d[n] for n, _ in N.ModelDesc._fields_])
+
+
+def _create(desc, world=1, nlx=None, emap=None):
+    E = desc.num_experts
+    emap = emap if emap is not None else [i // (E // world) for i in range(E)]
+    ep = N.EpDesc(world, 0, 0, 0, nlx if nlx is not None else E // world, 0,
+                  (C.c_int32 * len(emap))(*emap), (C.c_int32 * world)(*range(world)))
+    ctx = C.c_void_p()
+    rc = N.lib().fmoe_ctx_create(C.byref(desc), C.byref(ep), None, C.byref(ctx))
+    return rc, N.lib().fmoe_last_error().decode()
+
+
+@pytest.mark.parametrize("kw,code,needle", [
+    (dict(gpu_arch=900), 2, "sm_100a"),
+    (dict(token_dim=100), 1, "token dimension"),
+    (dict(ffn_size=72), 1, "Intermediate size"),
+    (dict(top_k=9), 1, "top_k"),
+    (dict(num_experts=12), 1, "multiple of 8"),
+    (dict(data_type=2), 2, "BF16 and FP16"),
+    (dict(expert_peer_capacity=0), 1, "expert_peer_capacity"),
+])
+def test_bad_descriptions_are_rejected(kw, code, needle):
+    rc, msg = _create(_desc(**kw))
+    assert rc == code, msg
+    assert needle in msg
+
+
+def test_bad_expert_maps_are_rejected():
+    rc, msg = _create(_desc(), world=2, emap=[0] * 8)
+    assert rc == 1 and "expert_map" in msg
+    rc, msg = _create(_desc(), world=2, nlx=3)
+    assert rc == 1
+
+
+def test_python_api_surface_matches_the_reference():
+    a = flashmoe.InitArgs(flashmoe.DataType.BF16, 1024, 5120, 8192, 16, 1, 1000, flashmoe.MLPType.GATED,
+                          flashmoe.ActivationType.SILU, 0, 0)
+    assert a.expert_peer_capacity == 64          # ceil(1024 / 16) * 1
+    assert a.ep_rank is None and a.expert_map is None
+    assert (int(flashmoe.MLPType.GATED), int(flashmoe.MLPType.VANILLA)) == (0, 1)
+    assert [int(x) for x in flashmoe.DataType] == [0, 1, 2, 3]
+    assert [int(x) for x in flashmoe.ActivationType] == [0, 1, 2, 3]
+    assert (int(flashmoe.Topology.NVLINK_ONLY), int(flashmoe.Topology.MIXED)) == (0, 1)
+    with pytest.raises(AssertionError):
+        flashmoe.ForwardArgs(flashmoe.MLPType.GATED, 1, 2, 3, 4, 5, 6, 7, 0)
+    f = flashmoe.ForwardArgs(flashmoe.MLPType.VANILLA, 1, 2, 3, 4, 5, 6, 7, 0)
+    assert f.local_expert_up_v is None and f.swish_alpha == 1.0
+    with pytest.raises(AssertionError):
+        flashmoe.InitArgs(flashmoe.DataType.BF16, 8, 64, 64, 8, 1, 600, 0, 0, 0, 0)
+    for name in ("initialize", "forward", "finalize", "router", "cb", "get_local_rank"):
+        assert hasattr(flashmoe, name)
+    for name in ("initialize", "forward", "finalize", "RouterForwardArgs"):
+        assert hasattr(flashmoe.router, name)
+
+
+def test_initialize_without_a_gpu_fails_loudly():
+    import torch
+    if torch.cuda.is_available():
+        pytest.skip("a GPU is present")
+    a = flashmoe.InitArgs(flashmoe.DataType.BF16, 128, 256, 256, 8, 2, 1000, flashmoe.MLPType.GATED,
+                          flashmoe.ActivationType.SILU, 0, 0)
+    with pytest.raises(flashmoe.FlashMoEError):
+        flashmoe.initialize(a)
