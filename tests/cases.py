@@ -21,13 +21,14 @@ GOLDEN_CASES = {
     "bf16_two_mtiles": Workload("bf16_two_mtiles", 400, 128, 128, 8, 2, D.BF16, M.GATED, A.SILU, seed=16,
                                 zipf_bias=True),
 }
-# router-only cases (any dtype the router takes)
+# router-only cases (any dtype the router takes; H is a multiple of 64 because the routing table
+# lives in an MoE context; 960 and 192 leave the router's last 32-lane pass ragged)
 ROUTER_CASES = {
     "r_fp32_e8_k2": Workload("r_fp32_e8_k2", 128, 1024, 64, 8, 2, D.FP32, seed=21),
     "r_bf16_e16_k1": Workload("r_bf16_e16_k1", 200, 512, 64, 16, 1, D.BF16, seed=22),
     "r_bf16_e128_k8": Workload("r_bf16_e128_k8", 130, 2048, 64, 128, 8, D.BF16, seed=23),
-    "r_bf16_e256_k8_zipf": Workload("r_bf16_e256_k8_zipf", 96, 1000 // 8 * 8, 64, 256, 8, D.BF16, seed=24,
+    "r_bf16_e256_k8_zipf": Workload("r_bf16_e256_k8_zipf", 96, 960, 64, 256, 8, D.BF16, seed=24,
                                     zipf_bias=True, capacity=6),
-    "r_fp16_e24_k3": Workload("r_fp16_e24_k3", 33, 136, 64, 24, 3, D.FP16, seed=25),
+    "r_fp16_e24_k3": Workload("r_fp16_e24_k3", 33, 192, 64, 24, 3, D.FP16, seed=25),
     "r_bf16_ties": Workload("r_bf16_ties", 64, 64, 64, 16, 4, D.BF16, seed=26),
 }
