@@ -74,6 +74,8 @@ SIGNATURES = {
                                      C.POINTER(C.c_void_p)]),
     "fmoe_router_forward": (C.c_int, [C.c_void_p, C.c_void_p, C.POINTER(RouterArgsC), C.c_void_p]),
     "fmoe_router_destroy": (C.c_int, [C.c_void_p, C.c_void_p]),
+    "fmoe_router_forward_static": (C.c_int, [C.POINTER(ModelDesc), C.c_int32, C.POINTER(RouterArgsC),
+                                            C.c_void_p, C.c_int32, C.c_void_p, C.c_void_p]),
     "fmoe_forward_host": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
                                     C.POINTER(RouterArgsC), C.POINTER(ForwardArgsC), C.c_void_p]),
     "fmoe_last_status": (C.c_int, [C.c_void_p, C.c_void_p, C.POINTER(Status)]),

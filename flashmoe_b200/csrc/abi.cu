@@ -12,7 +12,6 @@
 #include "common.cuh"
 
 namespace fmoe {
-namespace {
 
 thread_local std::string t_error;
 
@@ -20,6 +19,8 @@ int set_error(int code, const std::string& msg) {
   t_error = msg;
   return code;
 }
+
+namespace {
 
 #define FMOE_CUDA(expr)                                                                      \
   do {                                                                                       \
@@ -101,7 +102,7 @@ struct fmoe_router {
   float* topk_w = nullptr;
 };
 
-namespace {
+namespace fmoe {
 
 int validate_model(const fmoe_model_desc* m) {
   if (m == nullptr) return set_error(FMOE_ERR_INVALID_ARG, "model description is null");
@@ -131,6 +132,10 @@ int validate_model(const fmoe_model_desc* m) {
     return set_error(FMOE_ERR_UNSUPPORTED, "tokens_per_rank * top_k must stay below 2^26");
   return FMOE_OK;
 }
+
+}  // namespace fmoe
+
+namespace {
 
 void free_ctx(fmoe_ctx* c) {
   if (c == nullptr) return;

@@ -2,6 +2,7 @@
 #pragma once
 #include <cstddef>
 #include <cstdint>
+#include <string>
 #include <cuda.h>
 #include <cuda_runtime.h>
 
@@ -108,5 +109,9 @@ cudaError_t launch_moe(const MoeParams& p, const CUtensorMap* maps, int grid, si
                        cudaStream_t stream);
 
 extern unsigned long long g_launches;
+
+// host-side helpers shared by the translation units that export C entry points
+int set_error(int code, const std::string& msg);   // records the thread's last error text
+int validate_model(const fmoe_model_desc* m);
 
 }  // namespace fmoe

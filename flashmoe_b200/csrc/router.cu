@@ -20,6 +20,8 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
+#include <mutex>
+
 #include "common.cuh"
 
 namespace fmoe {
@@ -286,3 +288,82 @@ cudaError_t launch_router(const RouterParams& p, cudaStream_t stream) {
 }
 
 }  // namespace fmoe
+
+// ---- routing without any allocation ---------------------------------------------------------
+//
+// Some hosts of this library may not allocate device memory at all when they want a routing
+// decision: a serving engine that has handed the whole GPU to its own memory pool and treats any
+// later cudaMalloc as a bug (it can fail, and it synchronises the device), or a plug-in that is
+// called between two of the engine's own launches and must not disturb its allocator.  For them
+// the router's only scratch (the per-token top-k ids and weights the first kernel hands to the
+// second) lives in this fixed array instead of a per-context allocation.  Every GPU that loads
+// the library carries these 1 MiB until the process exits.
+constexpr int kStaticRouterMaxPairs = 1 << 17;  // tokens_per_rank * top_k this entry point accepts
+static __device__ __align__(256) unsigned char g_router_scratch[kStaticRouterMaxPairs * 8];
+
+namespace fmoe {
+namespace {
+std::mutex g_scratch_mu;
+constexpr int kMaxDevices = 64;
+void* g_scratch_addr[kMaxDevices] = {};  // device address of g_router_scratch, per device
+}  // namespace
+}  // namespace fmoe
+
+extern "C" int fmoe_router_forward_static(const fmoe_model_desc* model, int32_t device_id,
+                                          const fmoe_router_args* a, void* token_table,
+                                          int32_t round_ec, void* routes, void* stream) {
+  using namespace fmoe;
+  int rc = validate_model(model);
+  if (rc != FMOE_OK) return rc;
+  if (a == nullptr || a->tokens == nullptr || a->weights == nullptr || a->expert_counts == nullptr ||
+      token_table == nullptr || routes == nullptr)
+    return set_error(FMOE_ERR_INVALID_ARG, "tokens, weights, expert_counts, token_table and routes are required");
+  if (model->data_type == FMOE_DT_FP64)
+    return set_error(FMOE_ERR_UNSUPPORTED, "the router handles BF16, FP16 and FP32");
+  if ((reinterpret_cast<uintptr_t>(a->tokens) | reinterpret_cast<uintptr_t>(a->weights) |
+       reinterpret_cast<uintptr_t>(routes)) & 15)
+    return set_error(FMOE_ERR_INVALID_ARG, "tokens, weights and routes must be 16-byte aligned");
+  if (round_ec < model->expert_peer_capacity)
+    return set_error(FMOE_ERR_INVALID_ARG, "round_ec (row stride of token_table) is smaller than expert_peer_capacity");
+  const long long pairs = static_cast<long long>(model->tokens_per_rank) * model->top_k;
+  if (pairs > kStaticRouterMaxPairs)
+    return set_error(FMOE_ERR_UNSUPPORTED,
+                     "fmoe_router_forward_static handles at most " + std::to_string(kStaticRouterMaxPairs) +
+                         " (token, choice) pairs per call; this layer has " + std::to_string(pairs) +
+                         ": use fmoe_router_forward with a router context instead");
+  if (static_cast<size_t>(model->num_experts) * 4 * 8 * 4 > 200 * 1024)
+    return set_error(FMOE_ERR_UNSUPPORTED, "num_experts too large for the router's shared-memory rows");
+  if (device_id < 0 || device_id >= kMaxDevices)
+    return set_error(FMOE_ERR_INVALID_ARG, "device_id out of range");
+  cudaError_t ce = cudaSetDevice(device_id);
+  if (ce != cudaSuccess) return set_error(FMOE_ERR_CUDA, std::string("cudaSetDevice: ") + cudaGetErrorString(ce));
+  void* scratch = nullptr;
+  {
+    // One-time set-up per device, with that device current: the array's name is only a host-side
+    // stand-in for the symbol, the kernels need its device address.
+    std::lock_guard<std::mutex> lock(g_scratch_mu);
+    if (g_scratch_addr[device_id] == nullptr) {
+      void* addr = nullptr;
+      ce = cudaGetSymbolAddress(&addr, g_router_scratch);
+      if (ce != cudaSuccess || addr == nullptr)
+        return set_error(FMOE_ERR_CUDA, std::string("cudaGetSymbolAddress(router scratch): ") +
+                                            cudaGetErrorString(ce));
+      g_scratch_addr[device_id] = addr;
+    }
+    scratch = g_scratch_addr[device_id];
+  }
+  RouterParams p{};
+  p.S = model->tokens_per_rank; p.H = model->token_dim; p.E = model->num_experts; p.k = model->top_k;
+  p.EC = model->expert_peer_capacity; p.round_ec = round_ec; p.dtype = model->data_type;
+  p.tokens = a->tokens; p.weights = a->weights; p.logit_bias = a->logit_bias; p.routing = a->routing;
+  // both halves are fully rewritten for [0, pairs) by the first kernel before the second reads
+  // them, so nothing has to start at zero
+  p.topk_idx = static_cast<int32_t*>(scratch);
+  p.topk_w = reinterpret_cast<float*>(static_cast<unsigned char*>(scratch) + kStaticRouterMaxPairs * 4);
+  p.expert_counts = a->expert_counts;
+  p.table = static_cast<TokenSlot*>(token_table);
+  p.routes = static_cast<Route*>(routes);
+  ce = launch_router(p, static_cast<cudaStream_t>(stream));
+  if (ce != cudaSuccess) return set_error(FMOE_ERR_CUDA, std::string("router launch: ") + cudaGetErrorString(ce));
+  return FMOE_OK;
+}

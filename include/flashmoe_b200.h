@@ -153,6 +153,24 @@ int fmoe_router_forward(fmoe_router* router, fmoe_ctx* moe, const fmoe_router_ar
 /* Replaces finalizeGate / gate_finalize (bootstrap.cuh:434-447). */
 int fmoe_router_destroy(fmoe_router* router, void* stream);
 
+/* No counterpart in the reference.  The router for callers that must not allocate device memory
+ * (an engine whose memory pool owns the whole GPU, a plug-in running between the engine's own
+ * launches): same kernels and same results as fmoe_router_forward, but no router context and no
+ * cudaMalloc/cudaFree anywhere on the path.  The two scratch arrays the router needs live in a
+ * fixed device array inside the library (1 MiB per GPU that loads it, held until exit), which
+ * limits a call to tokens_per_rank * top_k <= 131072; larger layers get FMOE_ERR_UNSUPPORTED.
+ * The caller passes every input and output: `a->routing` is written when non-null, `token_table`
+ * is the [num_experts, round_ec] table of {uint32 token, float weight} (round_ec >=
+ * expert_peer_capacity), `routes` the [tokens_per_rank, top_k] records of {int32 expert, int32
+ * slot, float weight, int32 pad}, 16-byte aligned.  The first call on a device looks up the
+ * array's device address; make that call before any stream capture begins.  All calls on a device
+ * share the one array: it keeps the last call's contents (nothing in it has to start at zero), and
+ * two calls whose kernels overlap on the GPU (different streams, no ordering between them) race on
+ * it, so order them. */
+int fmoe_router_forward_static(const fmoe_model_desc* model, int32_t device_id,
+                               const fmoe_router_args* a, void* token_table, int32_t round_ec,
+                               void* routes, void* stream);
+
 /* The call sequence of quickstart.py:150-153 with HOST buffers: copies `tokens_host`
  * (pinned or pageable, [S, H] Element) to the device, runs router + forward, copies the
  * [S, H] result to `out_host` and synchronises `stream`.  `args->tokens`, `args->moe_out`
