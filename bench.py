@@ -155,7 +155,7 @@ def to_host(lw):
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--steps", type=int, default=1000)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--workload", default="scout")
     ap.add_argument("--tokens", type=int, default=None, help="override tokens_per_rank")
