@@ -308,9 +308,10 @@ def main() -> int:
         allc = [counts.tolist()]
     cap = w.expert_peer_capacity
     pairs_here = sum(min(c[e], cap) for c in allc for e in mine)
+    active = sum(1 for e in mine if any(c[e] > 0 for c in allc))   # experts whose weights are read
     c_mlp = 6 if w.mlp_type == MLPType.GATED else 4
     flops = float(pairs_here) * c_mlp * H * I
-    hbm_bytes = weight_bytes_per_rank(w, nlx) + 2.0 * S * H * eb
+    hbm_bytes = weight_bytes_per_rank(w, active) + 2.0 * S * H * eb
     t_tensor = flops / (peaks["bf16_tflops_sustained"] * 1e12)
     t_hbm = hbm_bytes / (peaks["hbm_gbs"] * 1e9)
     sec_kernel = ms_kernel * 1e-3
@@ -322,6 +323,7 @@ def main() -> int:
                 "frac": ach / peak, "peak_source": f"of {peaks_kind}",
                 "traffic": load_traffic(w.name, world), "ms_per_launch": ms_kernel,
                 "algorithmic_flops": flops, "algorithmic_hbm_bytes": hbm_bytes,
+                "active_local_experts": active, "routed_pairs": pairs_here,
                 "t_tensor_us": t_tensor * 1e6, "t_hbm_us": t_hbm * 1e6,
                 "pct_dense_bf16_peak_burst": 100.0 * flops / sec_kernel / (peaks["bf16_tflops"] * 1e12)}
 

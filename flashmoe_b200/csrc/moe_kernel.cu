@@ -15,7 +15,7 @@
 //    rank's per-expert counts first: each launch opens with a count exchange through the
 //    symmetric block (W*E ints per rank), which doubles as the epoch handshake.
 //  * No central "OS" CTA: every CTA runs the same scheduler warp, which takes tickets from one
-//    global counter over a fixed task order (GEMM0 of expert i, then GEMM1 of expert i-1)
+//    global counter over a fixed task order (GEMM0 of expert i, then GEMM1 of expert i-lag)
 //    and waits on the task's readiness counters itself.  Tickets are handed out in an order
 //    in which a task only ever waits on tasks with smaller tickets, so the kernel cannot
 //    deadlock as long as all CTAs are co-resident (grid <= SM count, one CTA per SM).
@@ -292,16 +292,21 @@ moe_forward_kernel(const __grid_constant__ MoeParams p, const __grid_constant__ 
     int mt = 0;
     for (int lx = 0; lx < nLx; ++lx) { tb.lx_mt0[lx] = mt; mt += (tb.lx_rows[lx] + kTileM - 1) / kTileM; }
     tb.lx_mt0[nLx] = mt;
-    // task order: G0(0), G0(1), G1(0), G0(2), G1(1), ..., G1(nLx-1)
+    // task order: GEMM1 of expert i trails GEMM0 of expert i by `lag` experts, the smallest lag
+    // whose GEMM0 tiles cover two tickets per CTA, so that by the time a GEMM1 ticket is drawn the
+    // GEMM0 tiles it depends on are long finished: G0(0..lag-1), G0(lag), G1(0), G0(lag+1), G1(1), ...
+    int lag = 1;
+    while (lag < nLx && tb.lx_mt0[lag] * p.tiles_n0 < 2 * static_cast<int>(gridDim.x)) ++lag;
     int ns = 0, first = 0;
-    for (int i = 0; i <= nLx; ++i) {
+    for (int i = 0; i < nLx + lag; ++i) {
       if (i < nLx) {
         tb.seg_first[ns] = first; tb.seg_kind[ns] = kTaskGemm0; tb.seg_lx[ns] = i; ++ns;
         first += (tb.lx_mt0[i + 1] - tb.lx_mt0[i]) * p.tiles_n0;
       }
-      if (i >= 1) {
-        tb.seg_first[ns] = first; tb.seg_kind[ns] = kTaskGemm1; tb.seg_lx[ns] = i - 1; ++ns;
-        first += (tb.lx_mt0[i] - tb.lx_mt0[i - 1]) * p.tiles_n1;
+      if (i >= lag) {
+        const int j = i - lag;
+        tb.seg_first[ns] = first; tb.seg_kind[ns] = kTaskGemm1; tb.seg_lx[ns] = j; ++ns;
+        first += (tb.lx_mt0[j + 1] - tb.lx_mt0[j]) * p.tiles_n1;
       }
     }
     tb.seg_first[ns] = first;

@@ -28,8 +28,6 @@ namespace fmoe {
 
 namespace {
 
-constexpr int kRouterWarps = 8;
-constexpr int kRouterThreads = kRouterWarps * 32;
 
 // 2^f on [-0.5, 0.5]: (ln 2)^k / k!, k = 0..7, rounded to fp32.
 __device__ __forceinline__ float det_exp(float x) {
@@ -96,19 +94,79 @@ struct Vec8<float> {
   }
 };
 
-// One warp owns TT consecutive tokens and walks the experts in groups of EG.
-template <typename T, int TT, int EG>
-__global__ void __launch_bounds__(kRouterThreads)
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gsrc) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(
+                   static_cast<uint32_t>(__cvta_generic_to_shared(smem_dst))),
+               "l"(gsrc)
+               : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
+template <typename T>
+__device__ __forceinline__ void vec8_from_smem(const T* p, float (&f)[8]);
+template <>
+__device__ __forceinline__ void vec8_from_smem<__nv_bfloat16>(const __nv_bfloat16* p, float (&f)[8]) {
+  const uint4 u = *reinterpret_cast<const uint4*>(p);
+  const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    f[2 * i] = __uint_as_float(w[i] << 16);
+    f[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+  }
+}
+template <>
+__device__ __forceinline__ void vec8_from_smem<__half>(const __half* p, float (&f)[8]) {
+  const uint4 u = *reinterpret_cast<const uint4*>(p);
+  const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 v = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
+    f[2 * i] = v.x;
+    f[2 * i + 1] = v.y;
+  }
+}
+template <>
+__device__ __forceinline__ void vec8_from_smem<float>(const float* p, float (&f)[8]) {
+  const float4 a = *reinterpret_cast<const float4*>(p);
+  const float4 b = *reinterpret_cast<const float4*>(p + 4);
+  f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w;
+  f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
+}
+
+// One warp owns TT consecutive tokens; the CTA walks the experts in groups of EG and the H axis
+// in chunks of 256 elements (one 8-element vector per lane).  The EG x 256 chunk of the router
+// weight is staged in shared memory (cp.async, double buffered) and shared by all warps, so the
+// weight matrix crosses L2 once per CTA instead of once per warp.
+template <typename T, int TT, int EG, int WARPS>
+__global__ void __launch_bounds__(WARPS * 32)
 router_topk_kernel(const RouterParams p) {
-  extern __shared__ float s_row[];  // [warps][TT][E]: logits, then exp, then probabilities
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int t0 = (blockIdx.x * kRouterWarps + warp) * TT;
-  if (t0 >= p.S) return;
+  extern __shared__ __align__(16) unsigned char s_raw[];
+  float* s_row = reinterpret_cast<float*>(s_raw);  // [WARPS][TT][E]: logits, then exp, then probabilities
   const int H = p.H, E = p.E;
+  T* wbuf = reinterpret_cast<T*>(s_raw + ((static_cast<size_t>(WARPS) * TT * E * sizeof(float) + 15) & ~size_t(15)));
+  constexpr int kChunk = 256;                       // elements of H per step
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int t0 = (blockIdx.x * WARPS + warp) * TT;
   const int nvec = H >> 3;
+  const int iters = (nvec + 31) >> 5;
   const T* __restrict__ X = static_cast<const T*>(p.tokens);
   const T* __restrict__ Wr = static_cast<const T*>(p.weights);
   float* rows = s_row + static_cast<size_t>(warp) * TT * E;
+
+  auto stage = [&](int eg, int it, int buf) {
+    const int v = it * 32 + lane;
+    if (v < nvec) {
+#pragma unroll
+      for (int e = warp; e < EG; e += WARPS)
+        cp_async16(wbuf + (static_cast<size_t>(buf) * EG + e) * kChunk + lane * 8,
+                   Wr + static_cast<size_t>(eg + e) * H + v * 8);
+    }
+    cp_async_commit();
+  };
 
   for (int eg = 0; eg < E; eg += EG) {
     float acc[TT][EG];
@@ -117,29 +175,37 @@ router_topk_kernel(const RouterParams p) {
 #pragma unroll
       for (int e = 0; e < EG; ++e) acc[t][e] = 0.0f;
 
-    for (int v = lane; v < nvec; v += 32) {
-      float xv[TT][8];
-#pragma unroll
-      for (int t = 0; t < TT; ++t) {
-        const int tok = min(t0 + t, p.S - 1);  // a ragged last group recomputes the last token
-        Vec8<T>::load(X + static_cast<size_t>(tok) * H + v * 8, xv[t]);
-      }
-#pragma unroll
-      for (int e = 0; e < EG; ++e) {
-        float wv[8];
-        Vec8<T>::load(Wr + static_cast<size_t>(eg + e) * H + v * 8, wv);
+    stage(eg, 0, 0);
+    for (int it = 0; it < iters; ++it) {
+      if (it + 1 < iters) { stage(eg, it + 1, (it + 1) & 1); cp_async_wait<1>(); } else { cp_async_wait<0>(); }
+      __syncthreads();
+      const int v = it * 32 + lane;
+      if (v < nvec) {
+        float xv[TT][8];
 #pragma unroll
         for (int t = 0; t < TT; ++t) {
+          const int tok = min(t0 + t, p.S - 1);  // ragged last group: recompute the last token
+          Vec8<T>::load(X + static_cast<size_t>(tok) * H + v * 8, xv[t]);
+        }
+        const T* wb = wbuf + static_cast<size_t>(it & 1) * EG * kChunk + lane * 8;
 #pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            if constexpr (Vec8<T>::kExactProducts) {
-              acc[t][e] = __fmaf_rn(xv[t][j], wv[j], acc[t][e]);
-            } else {
-              acc[t][e] = __fadd_rn(acc[t][e], __fmul_rn(xv[t][j], wv[j]));
+        for (int e = 0; e < EG; ++e) {
+          float wv[8];
+          vec8_from_smem<T>(wb + e * kChunk, wv);
+#pragma unroll
+          for (int t = 0; t < TT; ++t) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              if constexpr (Vec8<T>::kExactProducts) {
+                acc[t][e] = __fmaf_rn(xv[t][j], wv[j], acc[t][e]);
+              } else {
+                acc[t][e] = __fadd_rn(acc[t][e], __fmul_rn(xv[t][j], wv[j]));
+              }
             }
           }
         }
       }
+      __syncthreads();
     }
 #pragma unroll
     for (int t = 0; t < TT; ++t) {
@@ -154,6 +220,7 @@ router_topk_kernel(const RouterParams p) {
     }
   }
   __syncwarp();
+  if (t0 >= p.S) return;
 
   for (int t = 0; t < TT; ++t) {
     const int tok = t0 + t;
@@ -190,7 +257,7 @@ router_topk_kernel(const RouterParams p) {
         const int oi = __shfl_xor_sync(0xffffffffu, bi, off);
         if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
       }
-      if (bi == 0x7fffffff) bi = 0;  // nothing left to pick (k > E, or all NaN)
+      if (bi == 0x7fffffff) bi = 0;  // nothing left to pick (all NaN)
       if (lane == (bi & 31)) r[bi] = -INFINITY;
       wsum = __fadd_rn(wsum, bv);
       if (lane == (round & 31)) { my_p = bv; my_idx = bi; }
@@ -244,30 +311,33 @@ __global__ void __launch_bounds__(1024) router_slots_kernel(const RouterParams p
   if (threadIdx.x == 0) p.expert_counts[e] = base_s;
 }
 
-template <typename T, int TT>
+template <typename T, int TT, int WARPS>
 cudaError_t launch_topk_eg(const RouterParams& p, cudaStream_t stream) {
-  const int ctas = (p.S + kRouterWarps * TT - 1) / (kRouterWarps * TT);
-  const size_t smem = static_cast<size_t>(kRouterWarps) * TT * p.E * sizeof(float);
-  auto go = [&](auto kern) -> cudaError_t {
+  const int ctas = (p.S + WARPS * TT - 1) / (WARPS * TT);
+  auto go = [&](auto kern, int eg) -> cudaError_t {
+    const size_t rows = (static_cast<size_t>(WARPS) * TT * p.E * sizeof(float) + 15) & ~size_t(15);
+    const size_t smem = rows + 2 * static_cast<size_t>(eg) * 256 * sizeof(T);
     if (smem > 48 * 1024) {
       cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                            static_cast<int>(smem));
       if (e != cudaSuccess) return e;
     }
-    kern<<<ctas, kRouterThreads, smem, stream>>>(p);
+    kern<<<ctas, WARPS * 32, smem, stream>>>(p);
     ++g_launches;
     return cudaGetLastError();
   };
-  if (p.E % 32 == 0) return go(router_topk_kernel<T, TT, 32>);
-  if (p.E % 16 == 0) return go(router_topk_kernel<T, TT, 16>);
-  return go(router_topk_kernel<T, TT, 8>);
+  if (p.E % 32 == 0) return go(router_topk_kernel<T, TT, 32, WARPS>, 32);
+  if (p.E % 16 == 0) return go(router_topk_kernel<T, TT, 16, WARPS>, 16);
+  return go(router_topk_kernel<T, TT, 8, WARPS>, 8);
 }
 
+// Tokens per CTA = WARPS * TT: the largest that still gives about one CTA per SM.
 template <typename T>
 cudaError_t launch_topk(const RouterParams& p, cudaStream_t stream) {
-  if (p.S >= 3072) return launch_topk_eg<T, 4>(p, stream);
-  if (p.S >= 1536) return launch_topk_eg<T, 2>(p, stream);
-  return launch_topk_eg<T, 1>(p, stream);
+  if (p.S >= 120 * 32) return launch_topk_eg<T, 4, 8>(p, stream);
+  if (p.S >= 120 * 16) return launch_topk_eg<T, 4, 4>(p, stream);
+  if (p.S >= 120 * 8) return launch_topk_eg<T, 2, 4>(p, stream);
+  return launch_topk_eg<T, 1, 4>(p, stream);
 }
 
 }  // namespace

@@ -27,7 +27,7 @@ class RankLayout:
 
 
 def build(counts: Sequence[Sequence[int]], rank: int, expert_map: Sequence[int], ec: int,
-          tiles_n0: int, tiles_n1: int) -> RankLayout:
+          tiles_n0: int, tiles_n1: int, grid: int = 148) -> RankLayout:
     """counts[s][e] = tokens of rank s that chose expert e (unclamped, as the router writes them)."""
     W, E = len(counts), len(expert_map)
     nlx = E // W
@@ -46,14 +46,20 @@ def build(counts: Sequence[Sequence[int]], rank: int, expert_map: Sequence[int],
     mtile0 = [0]
     for lx in range(nlx):
         mtile0.append(mtile0[-1] + -(-lx_rows[lx] // TILE_M))
+    # GEMM1 of expert i trails GEMM0 of expert i by `lag` experts: the smallest lag whose GEMM0
+    # tiles cover two tickets per CTA
+    lag = 1
+    while lag < nlx and mtile0[lag] * tiles_n0 < 2 * grid:
+        lag += 1
     tasks = []
-    for i in range(nlx + 1):
+    for i in range(nlx + lag):
         if i < nlx:
             mts = mtile0[i + 1] - mtile0[i]
             tasks += [(0, i, m, n) for n in range(tiles_n0) for m in range(mts)]
-        if i >= 1:
-            mts = mtile0[i] - mtile0[i - 1]
-            tasks += [(1, i - 1, m, n) for n in range(tiles_n1) for m in range(mts)]
+        if i >= lag:
+            j = i - lag
+            mts = mtile0[j + 1] - mtile0[j]
+            tasks += [(1, j, m, n) for n in range(tiles_n1) for m in range(mts)]
     return RankLayout(sent, dst_row0, lx_base, lx_rows, mtile0, tasks)
 
 

@@ -122,7 +122,7 @@ def test_two_rank_exchange_matches_single_rank_oracle(name):
 
 def test_layout_matches_hand_computed_example():
     counts = [[3, 0, 130, 1], [2, 5, 0, 200]]
-    lay = layout.build(counts, 1, [0, 0, 1, 1], ec=128, tiles_n0=2, tiles_n1=1)
+    lay = layout.build(counts, 1, [0, 0, 1, 1], ec=128, tiles_n0=2, tiles_n1=1, grid=1)
     assert lay.sent == [[3, 0, 128, 1], [2, 5, 0, 128]]
     # owner 0: expert 0 has 5 rows at base 0, expert 1 has 5 rows at base 128;
     # owner 1: expert 2 has 128 rows at base 0, expert 3 has 129 rows at base 128
@@ -131,3 +131,6 @@ def test_layout_matches_hand_computed_example():
     assert lay.mtile0 == [0, 1, 3]
     kinds = [(t[0], t[1]) for t in lay.tasks]
     assert kinds == [(0, 0)] * 2 + [(0, 1)] * 4 + [(1, 0)] * 1 + [(1, 1)] * 2
+    # a wider grid makes GEMM1 trail by more experts: all GEMM0 tiles first here
+    wide = layout.build(counts, 1, [0, 0, 1, 1], ec=128, tiles_n0=2, tiles_n1=1, grid=148)
+    assert [(t[0], t[1]) for t in wide.tasks] == [(0, 0)] * 2 + [(0, 1)] * 4 + [(1, 0)] * 1 + [(1, 1)] * 2
