@@ -161,9 +161,14 @@ router_topk_kernel(const RouterParams p) {
     const int v = it * 32 + lane;
     if (v < nvec) {
 #pragma unroll
-      for (int e = warp; e < EG; e += WARPS)
-        cp_async16(wbuf + (static_cast<size_t>(buf) * EG + e) * kChunk + lane * 8,
-                   Wr + static_cast<size_t>(eg + e) * H + v * 8);
+      for (int e = warp; e < EG; e += WARPS) {
+        T* dst = wbuf + (static_cast<size_t>(buf) * EG + e) * kChunk + lane * 8;
+        const T* src = Wr + static_cast<size_t>(eg + e) * H + v * 8;
+#pragma unroll
+        for (int piece = 0; piece < static_cast<int>(sizeof(T)) * 8 / 16; ++piece)
+          cp_async16(reinterpret_cast<unsigned char*>(dst) + 16 * piece,
+                     reinterpret_cast<const unsigned char*>(src) + 16 * piece);
+      }
     }
     cp_async_commit();
   };
