@@ -92,6 +92,10 @@ struct fmoe_ctx {
   const void* map_src[3] = {nullptr, nullptr, nullptr};  // up, up_v, down the maps were built for
   void* stage_tokens = nullptr;         // host-buffer entry point staging
   void* stage_out = nullptr;
+  int eb = 2;                           // bytes per Element (4 for fp32 layers)
+  int planes = 1;                       // BF16 planes per GEMM operand (3 for fp32 layers)
+  char* wsplit = nullptr;               // fp32 layers: BF16 planes of up | up_v | down
+  size_t wsplit_up = 0, wsplit_up_v = 0, wsplit_down = 0;
 };
 
 struct fmoe_router {
@@ -143,6 +147,7 @@ void free_ctx(fmoe_ctx* c) {
     if (c->imported[r] && c->peers[r] != nullptr) cudaIpcCloseMemHandle(c->peers[r]);
   if (c->symm) cudaFree(c->symm);
   if (c->work) cudaFree(c->work);
+  if (c->wsplit) cudaFree(c->wsplit);
   if (c->stage_tokens) cudaFree(c->stage_tokens);
   if (c->stage_out) cudaFree(c->stage_out);
   delete c;
@@ -175,8 +180,8 @@ int fmoe_ctx_create(const fmoe_model_desc* model, const fmoe_ep_desc* ep, void* 
   int rc = validate_model(model);
   if (rc != FMOE_OK) return rc;
   if (ep == nullptr) return set_error(FMOE_ERR_INVALID_ARG, "ep description is null");
-  if (model->data_type != FMOE_DT_BF16 && model->data_type != FMOE_DT_FP16)
-    return set_error(FMOE_ERR_UNSUPPORTED, "the expert kernels handle BF16 and FP16; FP32/FP64 are not built yet");
+  if (model->data_type == FMOE_DT_FP64)
+    return set_error(FMOE_ERR_UNSUPPORTED, "the expert kernels handle BF16, FP16 and FP32; FP64 is not built");
   if (ep->topology != FMOE_TOPO_NVLINK_ONLY)
     return set_error(FMOE_ERR_UNSUPPORTED, "only Topology.NVLINK_ONLY (one NVLink box) is implemented");
   const int W = ep->ep_world, E = model->num_experts;
@@ -195,6 +200,8 @@ int fmoe_ctx_create(const fmoe_model_desc* model, const fmoe_ep_desc* ep, void* 
   if (c == nullptr) return set_error(FMOE_ERR_NO_MEMORY, "host allocation failed");
   c->model = *model;
   c->W = W; c->rank = ep->ep_rank; c->nLx = nLx; c->device = ep->device_id;
+  c->eb = model->data_type == FMOE_DT_FP32 ? 4 : 2;
+  c->planes = model->data_type == FMOE_DT_FP32 ? 3 : 1;
   c->owner.assign(ep->expert_map, ep->expert_map + E);
   c->lidx.assign(E, 0);
   c->local_e.assign(static_cast<size_t>(W) * nLx, -1);
@@ -240,8 +247,8 @@ int fmoe_ctx_create(const fmoe_model_desc* model, const fmoe_ep_desc* ep, void* 
   L.disp_arrived = off; off = align_up(off + sizeof(uint32_t) * W * nLx, 256);
   L.ret_arrived = off; off = align_up(off + sizeof(uint32_t), 256);
   L.landing_meta = off; off = align_up(off + sizeof(uint32_t) * g.landing_rows, 1024);
-  L.landing = off; off = align_up(off + static_cast<size_t>(g.landing_rows) * H * 2, 1024);
-  L.ret = off; off = align_up(off + static_cast<size_t>(S) * k * H * 2, 1024);
+  L.landing = off; off = align_up(off + static_cast<size_t>(c->planes) * g.landing_rows * H * 2, 1024);
+  L.ret = off; off = align_up(off + static_cast<size_t>(S) * k * H * c->eb, 1024);
   L.total = off;
   g.symm_bytes = static_cast<int64_t>(L.total);
 
@@ -256,7 +263,7 @@ int fmoe_ctx_create(const fmoe_model_desc* model, const fmoe_ep_desc* ep, void* 
   // private workspace
   const int max_mtiles = g.landing_rows / kTileM;
   size_t w = 0;
-  const size_t w_y = w; w = align_up(w + static_cast<size_t>(g.landing_rows) * I * 2, 1024);
+  const size_t w_y = w; w = align_up(w + static_cast<size_t>(c->planes) * g.landing_rows * I * 2, 1024);
   const size_t w_done = w; w = align_up(w + sizeof(uint32_t) * max_mtiles, 256);
   const size_t w_ctl = w; w = align_up(w + 256, 256);   // ticket, done_ctas, abort, epoch
   const size_t w_status = w; w = align_up(w + sizeof(fmoe_status), 256);
@@ -280,7 +287,8 @@ int fmoe_ctx_create(const fmoe_model_desc* model, const fmoe_ep_desc* ep, void* 
   MoeParams& p = c->params;
   p.S = S; p.H = H; p.I = I; p.E = E; p.k = k; p.EC = EC; p.round_ec = g.round_ec;
   p.W = W; p.rank = c->rank; p.nLx = nLx;
-  p.gated = gated ? 1 : 0; p.act = model->act_type; p.ab_format = model->data_type == FMOE_DT_BF16 ? 1 : 0;
+  p.gated = gated ? 1 : 0; p.act = model->act_type; p.ab_format = model->data_type == FMOE_DT_FP16 ? 0 : 1;
+  p.elem_bytes = c->eb;
   p.tiles_n0 = (I + g.tile_n0 - 1) / g.tile_n0;
   p.tiles_n1 = (H + g.tile_n1 - 1) / g.tile_n1;
   p.landing_rows = g.landing_rows; p.max_mtiles = max_mtiles;
@@ -298,8 +306,21 @@ int fmoe_ctx_create(const fmoe_model_desc* model, const fmoe_ep_desc* ep, void* 
   p.table = reinterpret_cast<const TokenSlot*>(c->work + w_table);
   p.routes = reinterpret_cast<const Route*>(c->work + w_routes);
 
-  rc = make_map(&c->maps[0], p.ab_format, c->symm + L.landing, g.landing_rows, H);
-  if (rc == FMOE_OK) rc = make_map(&c->maps[1], p.ab_format, p.y, g.landing_rows, I);
+  const uint64_t prow = static_cast<uint64_t>(c->planes) * g.landing_rows;
+  rc = make_map(&c->maps[0], p.ab_format, c->symm + L.landing, prow, H);
+  if (rc == FMOE_OK) rc = make_map(&c->maps[1], p.ab_format, p.y, prow, I);
+  if (rc == FMOE_OK && c->planes == 3) {
+    // fp32 layers: the weights are re-split into BF16 planes on every forward, into buffers the
+    // context owns, so their tensor maps are built once here
+    const size_t mat = static_cast<size_t>(nLx) * I * H * 2 * 3;
+    c->wsplit_up = 0; c->wsplit_up_v = gated ? mat : 0; c->wsplit_down = gated ? 2 * mat : mat;
+    ce = cudaMalloc(&c->wsplit, c->wsplit_down + mat);
+    if (ce != cudaSuccess) { free_ctx(c); return set_error(FMOE_ERR_NO_MEMORY, std::string("weight planes: ") + cudaGetErrorString(ce)); }
+    g.workspace_bytes += static_cast<int64_t>(c->wsplit_down + mat);
+    rc = make_map(&c->maps[2], 1, c->wsplit + c->wsplit_up, 3ull * nLx * I, H);
+    if (rc == FMOE_OK) rc = make_map(&c->maps[3], 1, c->wsplit + c->wsplit_up_v, 3ull * nLx * I, H);
+    if (rc == FMOE_OK) rc = make_map(&c->maps[4], 1, c->wsplit + c->wsplit_down, 3ull * nLx * H, I);
+  }
   if (rc != FMOE_OK) { free_ctx(c); return rc; }
   c->committed = (W == 1);
   if (W == 1) c->params.peers[0] = c->symm;
@@ -378,10 +399,10 @@ int fmoe_debug_buffer(fmoe_ctx* ctx, int32_t which, void** ptr_out, size_t* byte
     return set_error(FMOE_ERR_INVALID_ARG, "null argument");
   const MoeParams& p = ctx->params;
   switch (which) {
-    case 0: *ptr_out = ctx->symm + ctx->lay.landing; *bytes_out = static_cast<size_t>(p.landing_rows) * p.H * 2; break;
+    case 0: *ptr_out = ctx->symm + ctx->lay.landing; *bytes_out = static_cast<size_t>(ctx->planes) * p.landing_rows * p.H * 2; break;
     case 1: *ptr_out = ctx->symm + ctx->lay.landing_meta; *bytes_out = sizeof(uint32_t) * p.landing_rows; break;
-    case 2: *ptr_out = p.y; *bytes_out = static_cast<size_t>(p.landing_rows) * p.I * 2; break;
-    case 3: *ptr_out = ctx->symm + ctx->lay.ret; *bytes_out = static_cast<size_t>(p.S) * p.k * p.H * 2; break;
+    case 2: *ptr_out = p.y; *bytes_out = static_cast<size_t>(ctx->planes) * p.landing_rows * p.I * 2; break;
+    case 3: *ptr_out = ctx->symm + ctx->lay.ret; *bytes_out = static_cast<size_t>(p.S) * p.k * p.H * ctx->eb; break;
     case 4: *ptr_out = const_cast<Route*>(p.routes); *bytes_out = sizeof(Route) * p.S * p.k; break;
     default: return set_error(FMOE_ERR_INVALID_ARG, "unknown buffer id");
   }
@@ -409,7 +430,14 @@ int fmoe_forward(fmoe_ctx* ctx, const fmoe_forward_args* a, void* stream) {
     return set_error(FMOE_ERR_INVALID_ARG, "tokens, moe_out and the expert weights must be 16-byte aligned");
   MoeParams p = ctx->params;
   const void* up_v = gated ? a->local_expert_up_v : a->local_expert_up;
-  if (ctx->map_src[0] != a->local_expert_up || ctx->map_src[1] != up_v || ctx->map_src[2] != a->local_expert_down) {
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (ctx->planes == 3) {
+    const size_t n = static_cast<size_t>(p.nLx) * p.I * p.H;
+    FMOE_CUDA(launch_split_planes(static_cast<const float*>(a->local_expert_up), ctx->wsplit + ctx->wsplit_up, n, st));
+    if (gated)
+      FMOE_CUDA(launch_split_planes(static_cast<const float*>(a->local_expert_up_v), ctx->wsplit + ctx->wsplit_up_v, n, st));
+    FMOE_CUDA(launch_split_planes(static_cast<const float*>(a->local_expert_down), ctx->wsplit + ctx->wsplit_down, n, st));
+  } else if (ctx->map_src[0] != a->local_expert_up || ctx->map_src[1] != up_v || ctx->map_src[2] != a->local_expert_down) {
     int rc = make_map(&ctx->maps[2], p.ab_format, a->local_expert_up, static_cast<uint64_t>(p.nLx) * p.I, p.H);
     if (rc == FMOE_OK) rc = make_map(&ctx->maps[3], p.ab_format, up_v, static_cast<uint64_t>(p.nLx) * p.I, p.H);
     if (rc == FMOE_OK) rc = make_map(&ctx->maps[4], p.ab_format, a->local_expert_down, static_cast<uint64_t>(p.nLx) * p.H, p.I);
@@ -419,7 +447,7 @@ int fmoe_forward(fmoe_ctx* ctx, const fmoe_forward_args* a, void* stream) {
   p.tokens = a->tokens; p.expert_counts = a->expert_counts;
   p.bias_up = a->local_bias_up; p.bias_up_v = a->local_bias_up_v; p.bias_down = a->local_bias_down;
   p.out = a->moe_out; p.alpha = a->swish_alpha; p.beta = a->swish_beta;
-  FMOE_CUDA(launch_moe(p, ctx->maps, ctx->geo.grid, ctx->geo.smem_bytes, static_cast<cudaStream_t>(stream)));
+  FMOE_CUDA(launch_moe(p, ctx->maps, ctx->geo.grid, ctx->geo.smem_bytes, st));
   return FMOE_OK;
 }
 
@@ -498,7 +526,7 @@ int fmoe_forward_host(fmoe_ctx* ctx, fmoe_router* router, const void* tokens_hos
   if (ctx == nullptr || router == nullptr || tokens_host == nullptr || out_host == nullptr ||
       rargs == nullptr || args == nullptr)
     return set_error(FMOE_ERR_INVALID_ARG, "null argument");
-  const size_t bytes = static_cast<size_t>(ctx->params.S) * ctx->params.H * 2;
+  const size_t bytes = static_cast<size_t>(ctx->params.S) * ctx->params.H * ctx->eb;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (ctx->stage_tokens == nullptr) {
     FMOE_CUDA(cudaSetDevice(ctx->device));

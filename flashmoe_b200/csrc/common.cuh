@@ -54,7 +54,8 @@ struct SymmLayout {
 struct MoeParams {
   int S, H, I, E, k, EC, round_ec;
   int W, rank, nLx;
-  int gated, act, ab_format;  // ab_format: 0 fp16, 1 bf16
+  int gated, act, ab_format;  // ab_format: 0 fp16, 1 bf16 (fp32 layers run as BF16 planes)
+  int elem_bytes;             // 2, or 4 for fp32 layers
   int tiles_n0, tiles_n1;
   int landing_rows;
   int max_mtiles;
@@ -105,6 +106,7 @@ struct RouterParams {
 cudaError_t launch_router(const RouterParams& p, cudaStream_t stream);
 size_t moe_smem_bytes(int W, int E, int nLx);
 cudaError_t moe_prepare_kernel(size_t smem);
+cudaError_t launch_split_planes(const float* in, void* out, size_t n, cudaStream_t stream);
 cudaError_t launch_moe(const MoeParams& p, const CUtensorMap* maps, int grid, size_t smem,
                        cudaStream_t stream);
 

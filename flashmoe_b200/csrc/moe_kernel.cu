@@ -128,6 +128,66 @@ template <> struct Cvt<__half> {
   __device__ __forceinline__ static float round(float a) { return __half2float(__float2half_rn(a)); }
 };
 
+// FP32 layers run on the same BF16 tensor-core pipeline: every fp32 operand is held as three BF16
+// planes a = a1 + a2 + a3 (a1 = bf16(a), a2 = bf16(a - a1), a3 = bf16(a - a1 - a2), 24 mantissa
+// bits in all) and a product is the six plane pairs with i + j <= 2, accumulated in the fp32
+// TMEM accumulator.  The three dropped pairs are below 2^-24 relative.
+template <> struct Cvt<float> {
+  static constexpr int kFormat = 1;
+  __device__ __forceinline__ static float round(float a) { return a; }
+};
+template <typename T> struct Elem { static constexpr int kBytes = 2; static constexpr int kPlanes = 1; };
+template <> struct Elem<float> { static constexpr int kBytes = 4; static constexpr int kPlanes = 3; };
+
+__device__ __forceinline__ void split3(float a, unsigned short (&out)[3]) {
+  const __nv_bfloat16 a1 = __float2bfloat16_rn(a);
+  const float r1 = a - __bfloat162float(a1);
+  const __nv_bfloat16 a2 = __float2bfloat16_rn(r1);
+  const float r2 = r1 - __bfloat162float(a2);
+  const __nv_bfloat16 a3 = __float2bfloat16_rn(r2);
+  out[0] = __bfloat16_as_ushort(a1); out[1] = __bfloat16_as_ushort(a2); out[2] = __bfloat16_as_ushort(a3);
+}
+
+// 32 consecutive columns of one row of a GEMM operand buffer (Y): Element for 16-bit types, three
+// BF16 planes `plane_bytes` apart for fp32.  `row` points at the row's first column in plane 0.
+template <typename T>
+__device__ __forceinline__ void store_operand32(char* row, int col0, const float (&v)[32], size_t plane_bytes) {
+  if constexpr (Elem<T>::kPlanes == 1) {
+    uint4* dst = reinterpret_cast<uint4*>(row + static_cast<size_t>(col0) * 2);
+#pragma unroll
+    for (int q = 0; q < 4; ++q)
+      dst[q] = make_uint4(Cvt<T>::pack(v[8 * q], v[8 * q + 1]), Cvt<T>::pack(v[8 * q + 2], v[8 * q + 3]),
+                          Cvt<T>::pack(v[8 * q + 4], v[8 * q + 5]), Cvt<T>::pack(v[8 * q + 6], v[8 * q + 7]));
+  } else {
+    uint32_t pl[3][16];
+#pragma unroll
+    for (int i = 0; i < 32; i += 2) {
+      unsigned short a[3], b[3];
+      split3(v[i], a);
+      split3(v[i + 1], b);
+#pragma unroll
+      for (int q = 0; q < 3; ++q) pl[q][i >> 1] = static_cast<uint32_t>(a[q]) | (static_cast<uint32_t>(b[q]) << 16);
+    }
+#pragma unroll
+    for (int q = 0; q < 3; ++q) {
+      uint4* dst = reinterpret_cast<uint4*>(row + q * plane_bytes + static_cast<size_t>(col0) * 2);
+#pragma unroll
+      for (int w = 0; w < 4; ++w) dst[w] = make_uint4(pl[q][4 * w], pl[q][4 * w + 1], pl[q][4 * w + 2], pl[q][4 * w + 3]);
+    }
+  }
+}
+// 32 consecutive columns of one row of an Element buffer (the return rows).
+template <typename T>
+__device__ __forceinline__ void store_result32(char* row, int col0, const float (&v)[32]) {
+  if constexpr (Elem<T>::kBytes == 2) {
+    store_operand32<T>(row, col0, v, 0);
+  } else {
+    float4* dst = reinterpret_cast<float4*>(row + static_cast<size_t>(col0) * 4);
+#pragma unroll
+    for (int q = 0; q < 8; ++q) dst[q] = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+  }
+}
+
 __device__ __forceinline__ float activate(float x, int act) {
   switch (act) {
     case FMOE_ACT_SILU: return __fdividef(x, 1.0f + __expf(-x));
@@ -140,7 +200,11 @@ __device__ __forceinline__ float activate(float x, int act) {
 template <typename T>
 __device__ __forceinline__ float bias_at(const void* bias, size_t idx) {
   if (bias == nullptr) return 0.0f;
-  return Cvt<T>::up(static_cast<uint32_t>(__ldg(static_cast<const unsigned short*>(bias) + idx)));
+  if constexpr (Elem<T>::kBytes == 4) {
+    return __ldg(static_cast<const float*>(bias) + idx);
+  } else {
+    return Cvt<T>::up(static_cast<uint32_t>(__ldg(static_cast<const unsigned short*>(bias) + idx)));
+  }
 }
 
 // Shared-memory tables built by every CTA from the exchanged counts.
@@ -188,7 +252,10 @@ moe_forward_kernel(const __grid_constant__ MoeParams p, const __grid_constant__ 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int W = p.W, E = p.E, nLx = p.nLx;
   char* const self = p.peers[p.rank];
-  constexpr int EB = 2;  // bytes per element
+  constexpr int EB = Elem<T>::kBytes;     // bytes per element of tokens, return rows and output
+  constexpr int kPlanes = Elem<T>::kPlanes;  // BF16 planes per GEMM operand
+  const size_t landing_plane = static_cast<size_t>(p.landing_rows) * p.H * 2;
+  const size_t y_plane = static_cast<size_t>(p.landing_rows) * p.I * 2;
 
   // ---- set-up: barriers, TMEM, epoch ---------------------------------------------------
   if (tid == 0) {
@@ -340,8 +407,27 @@ moe_forward_kernel(const __grid_constant__ MoeParams p, const __grid_constant__ 
         const uint32_t token = p.table[static_cast<size_t>(e) * p.round_ec + j].token;
         const int drow = tb.dst_row0[e] + j;
         const uint4* src = tok_base + static_cast<size_t>(token) * vecs;
-        uint4* dst = reinterpret_cast<uint4*>(peer + p.lay.landing) + static_cast<size_t>(drow) * vecs;
-        for (int v = lane; v < vecs; v += 32) dst[v] = __ldg(src + v);
+        if constexpr (kPlanes == 1) {
+          uint4* dst = reinterpret_cast<uint4*>(peer + p.lay.landing) + static_cast<size_t>(drow) * vecs;
+          for (int v = lane; v < vecs; v += 32) dst[v] = __ldg(src + v);
+        } else {
+          // fp32 row -> three BF16 planes at the owner (4 floats in, 3 x 8 bytes out)
+          for (int v = lane; v < vecs; v += 32) {
+            const uint4 raw = __ldg(src + v);
+            const float f[4] = {__uint_as_float(raw.x), __uint_as_float(raw.y), __uint_as_float(raw.z),
+                                __uint_as_float(raw.w)};
+            unsigned short q[4][3];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) split3(f[i], q[i]);
+#pragma unroll
+            for (int pl = 0; pl < 3; ++pl) {
+              uint2* dst = reinterpret_cast<uint2*>(peer + p.lay.landing + pl * landing_plane) +
+                           static_cast<size_t>(drow) * vecs + v;
+              *dst = make_uint2(static_cast<uint32_t>(q[0][pl]) | (static_cast<uint32_t>(q[1][pl]) << 16),
+                                static_cast<uint32_t>(q[2][pl]) | (static_cast<uint32_t>(q[3][pl]) << 16));
+            }
+          }
+        }
         int choice = 0;
         if (lane < p.k) choice = (p.routes[static_cast<size_t>(token) * p.k + lane].expert == e) ? 1 : 0;
         const unsigned b = __ballot_sync(0xffffffffu, choice != 0);
@@ -362,6 +448,10 @@ moe_forward_kernel(const __grid_constant__ MoeParams p, const __grid_constant__ 
 
   // ---- expert GEMMs ---------------------------------------------------------------------
   const int nk0 = p.H / kTileK, nk1 = p.I / kTileK;
+  // plane pairs (A plane, B plane) per K block, smallest contributions first
+  constexpr int kPairs = kPlanes == 1 ? 1 : 6;
+  constexpr int kPairA[6] = {0, 2, 1, 0, 1, 0};
+  constexpr int kPairB[6] = {2, 0, 1, 1, 0, 0};
   if (ctl->ok && warp == 0) {
     if (lane == 0) {
       // scheduler + TMA producer
@@ -432,17 +522,21 @@ moe_forward_kernel(const __grid_constant__ MoeParams p, const __grid_constant__ 
         } else {
           brow0 = t.lx * p.H + t.n * 256; brow1 = brow0 + 128;
         }
-        for (int kb = 0; kb < nk; ++kb, ++fill) {
-          const uint32_t s = fill % kStages;
-          if (!mbar_wait(&ctl->empty[s], ((fill / kStages) & 1) ^ 1, p.abort_word)) {
-            fail(p, FMOE_PHASE_PIPE_EMPTY, ticket); ok = false; break;
+        const int b_plane_rows = g0 ? nLx * p.I : nLx * p.H;   // rows of one BF16 plane of the weights
+        for (int kb = 0; kb < nk && ok; ++kb) {
+          for (int pp = 0; pp < kPairs; ++pp, ++fill) {
+            const int pa = kPlanes == 1 ? 0 : kPairA[pp], pb = kPlanes == 1 ? 0 : kPairB[pp];
+            const uint32_t s = fill % kStages;
+            if (!mbar_wait(&ctl->empty[s], ((fill / kStages) & 1) ^ 1, p.abort_word)) {
+              fail(p, FMOE_PHASE_PIPE_EMPTY, ticket); ok = false; break;
+            }
+            uint8_t* sa = stages + s * kStageBytes;
+            uint8_t* sb = sa + kStageABytes;
+            mbar_expect_tx(&ctl->full[s], kStageBytes);
+            tma_load_2d(sa, map_a, &ctl->full[s], kb * kTileK, t.row0 + pa * p.landing_rows);
+            tma_load_2d(sb, map_b0, &ctl->full[s], kb * kTileK, brow0 + pb * b_plane_rows);
+            tma_load_2d(sb + kStageBBytes / 2, map_b1, &ctl->full[s], kb * kTileK, brow1 + pb * b_plane_rows);
           }
-          uint8_t* sa = stages + s * kStageBytes;
-          uint8_t* sb = sa + kStageABytes;
-          mbar_expect_tx(&ctl->full[s], kStageBytes);
-          tma_load_2d(sa, map_a, &ctl->full[s], kb * kTileK, t.row0);
-          tma_load_2d(sb, map_b0, &ctl->full[s], kb * kTileK, brow0);
-          tma_load_2d(sb + kStageBBytes / 2, map_b1, &ctl->full[s], kb * kTileK, brow1);
         }
       }
       if (!ok) {
@@ -463,7 +557,7 @@ moe_forward_kernel(const __grid_constant__ MoeParams p, const __grid_constant__ 
         const Task t = ctl->tasks[tslot];
         mbar_arrive(&ctl->task_empty[tslot]);
         if (t.kind == kTaskStop) break;
-        const int nk = t.kind == kTaskGemm0 ? nk0 : nk1;
+        const int nk = (t.kind == kTaskGemm0 ? nk0 : nk1) * kPairs;
         const uint32_t buf = acc_it % kAccBufs;
         if (!mbar_wait(&ctl->acc_empty[buf], ((acc_it / kAccBufs) & 1) ^ 1, p.abort_word)) {
           fail(p, FMOE_PHASE_TMEM_EMPTY, t.mt); break;
@@ -514,7 +608,7 @@ moe_forward_kernel(const __grid_constant__ MoeParams p, const __grid_constant__ 
       const int row = t.row0 + row_in_tile;
 
       if (t.kind == kTaskGemm0) {
-        uint4* yrow = reinterpret_cast<uint4*>(static_cast<char*>(p.y) + static_cast<size_t>(row) * p.I * EB);
+        char* yrow = static_cast<char*>(p.y) + static_cast<size_t>(row) * p.I * 2;
         if (p.gated) {
           const int col_base = t.n * 128;
 #pragma unroll 1
@@ -526,24 +620,16 @@ moe_forward_kernel(const __grid_constant__ MoeParams p, const __grid_constant__ 
             tmem_ld_wait();
             const int col0 = col_base + c * 32;
             if (valid && col0 < p.I) {
-              uint32_t packed[16];
+              float y[32];
 #pragma unroll
-              for (int i = 0; i < 32; i += 2) {
-                float y2[2];
-#pragma unroll
-                for (int h = 0; h < 2; ++h) {
-                  const size_t bi = static_cast<size_t>(t.lx) * p.I + col0 + i + h;
-                  const float gate = (__uint_as_float(g[i + h]) + bias_at<T>(p.bias_up, bi)) * p.beta;
-                  const float tt = Cvt<T>::round(p.alpha * activate(gate, p.act));
-                  const float v = __uint_as_float(u[i + h]) + bias_at<T>(p.bias_up_v, bi);
-                  y2[h] = v * tt;
-                }
-                packed[i >> 1] = Cvt<T>::pack(y2[0], y2[1]);
+              for (int i = 0; i < 32; ++i) {
+                const size_t bi = static_cast<size_t>(t.lx) * p.I + col0 + i;
+                const float gate = (__uint_as_float(g[i]) + bias_at<T>(p.bias_up, bi)) * p.beta;
+                const float tt = Cvt<T>::round(p.alpha * activate(gate, p.act));
+                const float v = __uint_as_float(u[i]) + bias_at<T>(p.bias_up_v, bi);
+                y[i] = v * tt;
               }
-              uint4* dst = yrow + (col0 * EB) / 16;
-#pragma unroll
-              for (int v = 0; v < 4; ++v)
-                dst[v] = make_uint4(packed[4 * v], packed[4 * v + 1], packed[4 * v + 2], packed[4 * v + 3]);
+              store_operand32<T>(yrow, col0, y, y_plane);
             }
           }
         } else {
@@ -556,18 +642,13 @@ moe_forward_kernel(const __grid_constant__ MoeParams p, const __grid_constant__ 
             tmem_ld_wait();
             const int col0 = col_base + c * 32;
             if (valid && col0 < p.I) {
-              uint32_t packed[16];
+              float y[32];
 #pragma unroll
-              for (int i = 0; i < 32; i += 2) {
+              for (int i = 0; i < 32; ++i) {
                 const size_t bi = static_cast<size_t>(t.lx) * p.I + col0 + i;
-                const float y0 = activate(__uint_as_float(a[i]) + bias_at<T>(p.bias_up, bi), p.act);
-                const float y1 = activate(__uint_as_float(a[i + 1]) + bias_at<T>(p.bias_up, bi + 1), p.act);
-                packed[i >> 1] = Cvt<T>::pack(y0, y1);
+                y[i] = activate(__uint_as_float(a[i]) + bias_at<T>(p.bias_up, bi), p.act);
               }
-              uint4* dst = yrow + (col0 * EB) / 16;
-#pragma unroll
-              for (int v = 0; v < 4; ++v)
-                dst[v] = make_uint4(packed[4 * v], packed[4 * v + 1], packed[4 * v + 2], packed[4 * v + 3]);
+              store_operand32<T>(yrow, col0, y, y_plane);
             }
           }
         }
@@ -583,8 +664,7 @@ moe_forward_kernel(const __grid_constant__ MoeParams p, const __grid_constant__ 
         if (valid) meta = __ldcg(reinterpret_cast<const uint32_t*>(self + p.lay.landing_meta) + row);
         const int src = static_cast<int>(meta >> kMetaSrcShift);
         const uint32_t ret_row = meta & ((1u << kMetaSrcShift) - 1);
-        uint4* orow = reinterpret_cast<uint4*>(p.peers[valid ? src : p.rank] + p.lay.ret +
-                                               static_cast<size_t>(ret_row) * p.H * EB);
+        char* orow = p.peers[valid ? src : p.rank] + p.lay.ret + static_cast<size_t>(ret_row) * p.H * EB;
         const int col_base = t.n * 256;
 #pragma unroll 1
         for (int c = 0; c < 8; ++c) {
@@ -594,18 +674,11 @@ moe_forward_kernel(const __grid_constant__ MoeParams p, const __grid_constant__ 
           tmem_ld_wait();
           const int col0 = col_base + c * 32;
           if (valid && col0 < p.H) {
-            uint32_t packed[16];
+            float o[32];
 #pragma unroll
-            for (int i = 0; i < 32; i += 2) {
-              const size_t bi = static_cast<size_t>(t.lx) * p.H + col0 + i;
-              const float o0 = __uint_as_float(a[i]) + bias_at<T>(p.bias_down, bi);
-              const float o1 = __uint_as_float(a[i + 1]) + bias_at<T>(p.bias_down, bi + 1);
-              packed[i >> 1] = Cvt<T>::pack(o0, o1);
-            }
-            uint4* dst = orow + (col0 * EB) / 16;
-#pragma unroll
-            for (int v = 0; v < 4; ++v)
-              dst[v] = make_uint4(packed[4 * v], packed[4 * v + 1], packed[4 * v + 2], packed[4 * v + 3]);
+            for (int i = 0; i < 32; ++i)
+              o[i] = __uint_as_float(a[i]) + bias_at<T>(p.bias_down, static_cast<size_t>(t.lx) * p.H + col0 + i);
+            store_result32<T>(orow, col0, o);
           }
         }
         tc_fence_before_sync();
@@ -650,23 +723,35 @@ moe_forward_kernel(const __grid_constant__ MoeParams p, const __grid_constant__ 
         }
       } else {
         for (int v = lane; v < vecs; v += 32) {
-          float acc[8];
+          constexpr int kPer = 16 / EB;   // elements per 16-byte vector
+          float acc[kPer];
 #pragma unroll
-          for (int i = 0; i < 8; ++i) acc[i] = 0.0f;
+          for (int i = 0; i < kPer; ++i) acc[i] = 0.0f;
           for (int j = 0; j < p.k; ++j) {
             const Route r = p.routes[static_cast<size_t>(tkn) * p.k + j];
             if (r.slot >= p.EC) continue;
             const uint4 x = __ldcg(ret + (static_cast<size_t>(tkn) * p.k + j) * vecs + v);
             const uint32_t w4[4] = {x.x, x.y, x.z, x.w};
+            if constexpr (EB == 2) {
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              acc[2 * i] = __fadd_rn(acc[2 * i], __fmul_rn(Cvt<T>::up(w4[i] & 0xffffu), r.weight));
-              acc[2 * i + 1] = __fadd_rn(acc[2 * i + 1], __fmul_rn(Cvt<T>::up(w4[i] >> 16), r.weight));
+              for (int i = 0; i < 4; ++i) {
+                acc[2 * i] = __fadd_rn(acc[2 * i], __fmul_rn(Cvt<T>::up(w4[i] & 0xffffu), r.weight));
+                acc[2 * i + 1] = __fadd_rn(acc[2 * i + 1], __fmul_rn(Cvt<T>::up(w4[i] >> 16), r.weight));
+              }
+            } else {
+#pragma unroll
+              for (int i = 0; i < 4; ++i) acc[i] = __fadd_rn(acc[i], __fmul_rn(__uint_as_float(w4[i]), r.weight));
             }
           }
-          out[static_cast<size_t>(tkn) * vecs + v] =
-              make_uint4(Cvt<T>::pack(acc[0], acc[1]), Cvt<T>::pack(acc[2], acc[3]),
-                         Cvt<T>::pack(acc[4], acc[5]), Cvt<T>::pack(acc[6], acc[7]));
+          if constexpr (EB == 2) {
+            out[static_cast<size_t>(tkn) * vecs + v] =
+                make_uint4(Cvt<T>::pack(acc[0], acc[1]), Cvt<T>::pack(acc[2], acc[3]),
+                           Cvt<T>::pack(acc[4], acc[5]), Cvt<T>::pack(acc[6], acc[7]));
+          } else {
+            out[static_cast<size_t>(tkn) * vecs + v] =
+                make_uint4(__float_as_uint(acc[0]), __float_as_uint(acc[1]), __float_as_uint(acc[2]),
+                           __float_as_uint(acc[3]));
+          }
         }
       }
     }
@@ -698,15 +783,41 @@ cudaError_t moe_prepare_kernel(size_t smem) {
                                        cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        static_cast<int>(smem));
   if (e != cudaSuccess) return e;
-  return cudaFuncSetAttribute(moe_forward_kernel<__half>,
-                              cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+  e = cudaFuncSetAttribute(moe_forward_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                           static_cast<int>(smem));
+  if (e != cudaSuccess) return e;
+  return cudaFuncSetAttribute(moe_forward_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                              static_cast<int>(smem));
+}
+
+namespace {
+// fp32 [n] -> three BF16 planes [3][n] (see Cvt<float>)
+__global__ void split_planes_kernel(const float* __restrict__ in, unsigned short* __restrict__ out, size_t n) {
+  const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
+  for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride) {
+    unsigned short q[3];
+    split3(__ldg(in + i), q);
+    out[i] = q[0]; out[n + i] = q[1]; out[2 * n + i] = q[2];
+  }
+}
+}  // namespace
+
+cudaError_t launch_split_planes(const float* in, void* out, size_t n, cudaStream_t stream) {
+  const int threads = 256;
+  const size_t want = (n + threads - 1) / threads;
+  const int blocks = static_cast<int>(want < 148 * 16 ? (want ? want : 1) : 148 * 16);
+  split_planes_kernel<<<blocks, threads, 0, stream>>>(in, static_cast<unsigned short*>(out), n);
+  ++g_launches;
+  return cudaGetLastError();
 }
 
 cudaError_t launch_moe(const MoeParams& p, const CUtensorMap* maps, int grid, size_t smem,
                        cudaStream_t stream) {
   TmaMaps m;
   m.landing = maps[0]; m.y = maps[1]; m.up = maps[2]; m.up_v = maps[3]; m.down = maps[4];
-  if (p.ab_format == 1) {
+  if (p.elem_bytes == 4) {
+    moe_forward_kernel<float><<<grid, kThreads, smem, stream>>>(p, m);
+  } else if (p.ab_format == 1) {
     moe_forward_kernel<__nv_bfloat16><<<grid, kThreads, smem, stream>>>(p, m);
   } else {
     moe_forward_kernel<__half><<<grid, kThreads, smem, stream>>>(p, m);

@@ -17,6 +17,11 @@ GOLDEN_CASES = {
                                      A.GELU, seed=14, bias_std=0.1),
     # fp16, ReLU
     "fp16_gated_relu": Workload("fp16_gated_relu", 50, 192, 320, 8, 2, D.FP16, M.GATED, A.RELU, seed=15),
+    # fp32 layers (three BF16 planes per operand on the tensor cores), tolerance 1e-5
+    "fp32_gated_k2": Workload("fp32_gated_k2", 96, 256, 384, 8, 2, D.FP32, M.GATED, A.SILU, seed=17,
+                              bias_std=0.2),
+    "fp32_vanilla_gelu_k4": Workload("fp32_vanilla_gelu_k4", 80, 192, 256, 16, 4, D.FP32, M.VANILLA, A.GELU,
+                                     seed=18),
     # an expert with more than one M tile of rows
     "bf16_two_mtiles": Workload("bf16_two_mtiles", 400, 128, 128, 8, 2, D.BF16, M.GATED, A.SILU, seed=16,
                                 zipf_bias=True),

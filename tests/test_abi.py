@@ -57,7 +57,7 @@ def _create(desc, world=1, nlx=None, emap=None):
     (dict(ffn_size=72), 1, "Intermediate size"),
     (dict(top_k=9), 1, "top_k"),
     (dict(num_experts=12), 1, "multiple of 8"),
-    (dict(data_type=2), 2, "BF16 and FP16"),
+    (dict(data_type=3), 2, "FP64 is not built"),
     (dict(expert_peer_capacity=0), 1, "expert_peer_capacity"),
 ])
 def test_bad_descriptions_are_rejected(kw, code, needle):

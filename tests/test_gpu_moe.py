@@ -34,7 +34,24 @@ def test_forward_matches_oracle_and_golden(name):
         # a second and third launch on the same context (epoch protocol, no host-side clearing)
         for _ in range(2):
             again = layer.forward(x).cpu()
-            assert torch.equal(again.view(torch.int16), out.view(torch.int16))
+            assert torch.equal(again, out)
+    finally:
+        layer.close()
+
+
+def test_fp32_reference_configuration():
+    """The benchmark description's first configuration: FP32, 128 tokens, H=1024, I=2048, E=8, k=2,
+    gated SiLU, one rank; tolerance 1e-5 of the output's largest magnitude."""
+    w = CONFIGS["cpu_ref_fp32"]
+    lw, x = make_weights(w), make_tokens(w)
+    ref, r = oracle_layer(w, x=x, lw=lw)
+    layer = make_layer(w, lw)
+    try:
+        out = layer.forward(x).cpu()
+        assert max_rel_err(out, ref) <= 1e-5, max_rel_err(out, ref)
+        dense = O.dense_f64(x, r, oracle_weights(lw), w.top_k, w.expert_peer_capacity, int(w.mlp_type),
+                            int(w.act_type))
+        assert max_rel_err(out, dense) <= 1e-5, max_rel_err(out, dense)
     finally:
         layer.close()
 
