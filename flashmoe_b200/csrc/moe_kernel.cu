@@ -130,8 +130,11 @@ template <> struct Cvt<__half> {
 
 // FP32 layers run on the same BF16 tensor-core pipeline: every fp32 operand is held as three BF16
 // planes a = a1 + a2 + a3 (a1 = bf16(a), a2 = bf16(a - a1), a3 = bf16(a - a1 - a2), 24 mantissa
-// bits in all) and a product is the six plane pairs with i + j <= 2, accumulated in the fp32
-// TMEM accumulator.  The three dropped pairs are below 2^-24 relative.
+// bits in all) and a product is the six plane pairs with i + j <= 2.  The three dropped pairs are
+// below 2^-24 relative.  The leading pair (a1, b1) accumulates in one TMEM accumulator and the five
+// correction pairs in a second one; the epilogue adds the two in fp32.  Keeping the corrections
+// apart matters: the tensor core's accumulate step is not correctly rounded, and its error scales
+// with the accumulator's magnitude and with the number of MMA steps into it.
 template <> struct Cvt<float> {
   static constexpr int kFormat = 1;
   __device__ __forceinline__ static float round(float a) { return a; }
@@ -188,9 +191,12 @@ __device__ __forceinline__ void store_result32(char* row, int col0, const float 
   }
 }
 
-__device__ __forceinline__ float activate(float x, int act) {
+template <bool kPrecise>
+__device__ __forceinline__ float activate_t(float x, int act) {
   switch (act) {
-    case FMOE_ACT_SILU: return __fdividef(x, 1.0f + __expf(-x));
+    case FMOE_ACT_SILU:
+      if constexpr (kPrecise) return x / (1.0f + expf(-x));
+      else return __fdividef(x, 1.0f + __expf(-x));
     case FMOE_ACT_GELU: return 0.5f * x * (1.0f + erff(x * 0.70710678118654752f));
     case FMOE_ACT_RELU: return fmaxf(x, 0.0f);
     default: return x;
@@ -450,6 +456,7 @@ moe_forward_kernel(const __grid_constant__ MoeParams p, const __grid_constant__ 
   const int nk0 = p.H / kTileK, nk1 = p.I / kTileK;
   // plane pairs (A plane, B plane) per K block, smallest contributions first
   constexpr int kPairs = kPlanes == 1 ? 1 : 6;
+  constexpr int kBufs = kPlanes == 1 ? kAccBufs : 1;   // fp32 layers use both TMEM halves per task
   constexpr int kPairA[6] = {0, 2, 1, 0, 1, 0};
   constexpr int kPairB[6] = {2, 0, 1, 1, 0, 0};
   if (ctl->ok && warp == 0) {
@@ -558,12 +565,13 @@ moe_forward_kernel(const __grid_constant__ MoeParams p, const __grid_constant__ 
         mbar_arrive(&ctl->task_empty[tslot]);
         if (t.kind == kTaskStop) break;
         const int nk = (t.kind == kTaskGemm0 ? nk0 : nk1) * kPairs;
-        const uint32_t buf = acc_it % kAccBufs;
-        if (!mbar_wait(&ctl->acc_empty[buf], ((acc_it / kAccBufs) & 1) ^ 1, p.abort_word)) {
+        const uint32_t buf = acc_it % kBufs;
+        if (!mbar_wait(&ctl->acc_empty[buf], ((acc_it / kBufs) & 1) ^ 1, p.abort_word)) {
           fail(p, FMOE_PHASE_TMEM_EMPTY, t.mt); break;
         }
         tc_fence_after_sync();
         const uint32_t d_tmem = ctl->tmem_base + buf * kUmmaN;
+        const uint32_t d_corr = ctl->tmem_base + kUmmaN;   // fp32 layers only (single-buffered there)
         bool ok = true;
         for (int kb = 0; kb < nk; ++kb, ++fill) {
           const uint32_t s = fill % kStages;
@@ -573,10 +581,14 @@ moe_forward_kernel(const __grid_constant__ MoeParams p, const __grid_constant__ 
           tc_fence_after_sync();
           const uint32_t a_addr = smem_u32(stages + s * kStageBytes);
           const uint32_t b_addr = a_addr + kStageABytes;
+          // fp32 layers: the last pair of every K block is the leading one (planes 0 x 0)
+          const bool lead = kPlanes == 1 || (kb % kPairs) == kPairs - 1;
+          const uint32_t d = lead ? d_tmem : d_corr;
+          const bool first = lead ? (kb < kPairs) : (kb == 0);
 #pragma unroll
           for (int k = 0; k < kTileK / 16; ++k) {
-            umma_f16(d_tmem, umma_desc_sw128(a_addr + k * 32), umma_desc_sw128(b_addr + k * 32),
-                     idesc, (kb > 0 || k > 0) ? 1u : 0u);
+            umma_f16(d, umma_desc_sw128(a_addr + k * 32), umma_desc_sw128(b_addr + k * 32),
+                     idesc, (!first || k > 0) ? 1u : 0u);
           }
           umma_commit(&ctl->empty[s]);
         }
@@ -598,8 +610,8 @@ moe_forward_kernel(const __grid_constant__ MoeParams p, const __grid_constant__ 
       __syncwarp();
       if (lane == 0) mbar_arrive(&ctl->task_empty[tslot]);
       if (t.kind == kTaskStop) break;
-      const uint32_t buf = acc_it % kAccBufs;
-      if (!mbar_wait(&ctl->acc_full[buf], (acc_it / kAccBufs) & 1, p.abort_word)) {
+      const uint32_t buf = acc_it % kBufs;
+      if (!mbar_wait(&ctl->acc_full[buf], (acc_it / kBufs) & 1, p.abort_word)) {
         fail(p, FMOE_PHASE_TMEM_FULL, t.mt); break;
       }
       tc_fence_after_sync();
@@ -618,6 +630,17 @@ moe_forward_kernel(const __grid_constant__ MoeParams p, const __grid_constant__ 
             tmem_ld_32x32(taddr + c * 32, g);
             tmem_ld_32x32(taddr + 128 + c * 32, u);
             tmem_ld_wait();
+            if constexpr (kPlanes == 3) {
+              uint32_t cg[32], cu[32];
+              tmem_ld_32x32(taddr + kUmmaN + c * 32, cg);
+              tmem_ld_32x32(taddr + kUmmaN + 128 + c * 32, cu);
+              tmem_ld_wait();
+#pragma unroll
+              for (int i = 0; i < 32; ++i) {
+                g[i] = __float_as_uint(__uint_as_float(g[i]) + __uint_as_float(cg[i]));
+                u[i] = __float_as_uint(__uint_as_float(u[i]) + __uint_as_float(cu[i]));
+              }
+            }
             const int col0 = col_base + c * 32;
             if (valid && col0 < p.I) {
               float y[32];
@@ -625,7 +648,7 @@ moe_forward_kernel(const __grid_constant__ MoeParams p, const __grid_constant__ 
               for (int i = 0; i < 32; ++i) {
                 const size_t bi = static_cast<size_t>(t.lx) * p.I + col0 + i;
                 const float gate = (__uint_as_float(g[i]) + bias_at<T>(p.bias_up, bi)) * p.beta;
-                const float tt = Cvt<T>::round(p.alpha * activate(gate, p.act));
+                const float tt = Cvt<T>::round(p.alpha * activate_t<EB == 4>(gate, p.act));
                 const float v = __uint_as_float(u[i]) + bias_at<T>(p.bias_up_v, bi);
                 y[i] = v * tt;
               }
@@ -640,13 +663,20 @@ moe_forward_kernel(const __grid_constant__ MoeParams p, const __grid_constant__ 
             __syncwarp();
             tmem_ld_32x32(taddr + c * 32, a);
             tmem_ld_wait();
+            if constexpr (kPlanes == 3) {
+              uint32_t ca[32];
+              tmem_ld_32x32(taddr + kUmmaN + c * 32, ca);
+              tmem_ld_wait();
+#pragma unroll
+              for (int i = 0; i < 32; ++i) a[i] = __float_as_uint(__uint_as_float(a[i]) + __uint_as_float(ca[i]));
+            }
             const int col0 = col_base + c * 32;
             if (valid && col0 < p.I) {
               float y[32];
 #pragma unroll
               for (int i = 0; i < 32; ++i) {
                 const size_t bi = static_cast<size_t>(t.lx) * p.I + col0 + i;
-                y[i] = activate(__uint_as_float(a[i]) + bias_at<T>(p.bias_up, bi), p.act);
+                y[i] = activate_t<EB == 4>(__uint_as_float(a[i]) + bias_at<T>(p.bias_up, bi), p.act);
               }
               store_operand32<T>(yrow, col0, y, y_plane);
             }
@@ -672,6 +702,13 @@ moe_forward_kernel(const __grid_constant__ MoeParams p, const __grid_constant__ 
           __syncwarp();
           tmem_ld_32x32(taddr + c * 32, a);
           tmem_ld_wait();
+          if constexpr (kPlanes == 3) {
+            uint32_t ca[32];
+            tmem_ld_32x32(taddr + kUmmaN + c * 32, ca);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) a[i] = __float_as_uint(__uint_as_float(a[i]) + __uint_as_float(ca[i]));
+          }
           const int col0 = col_base + c * 32;
           if (valid && col0 < p.H) {
             float o[32];
