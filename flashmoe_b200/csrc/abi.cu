@@ -4,6 +4,7 @@
 // (csrc/include/flashmoe/bootstrap.cuh:197-474) and of its pybind glue
 // (flashmoe/bindings.py:68-185, 238-315), with CUDA IPC in place of the NVSHMEM heap.
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <new>
 #include <string>
@@ -235,7 +236,7 @@ int fmoe_ctx_create(const fmoe_model_desc* model, const fmoe_ep_desc* ep, void* 
   const long long cap_b = static_cast<long long>(align_up(static_cast<size_t>(W) * S * k, kTileM)) +
                           static_cast<long long>(nLx) * kTileM;
   g.landing_rows = static_cast<int>(cap_a < cap_b ? cap_a : cap_b);
-  g.grid = sms; g.threads = kThreads;
+  g.grid = sms & ~1; g.threads = kThreads;   // CTA pairs: an even number of CTAs, one per SM
   g.smem_bytes = static_cast<int>(moe_smem_bytes(W, E, nLx));
   if (g.smem_bytes > 227 * 1024) { free_ctx(c); return set_error(FMOE_ERR_UNSUPPORTED, "tables do not fit in shared memory"); }
 
@@ -289,6 +290,7 @@ int fmoe_ctx_create(const fmoe_model_desc* model, const fmoe_ep_desc* ep, void* 
   p.W = W; p.rank = c->rank; p.nLx = nLx;
   p.gated = gated ? 1 : 0; p.act = model->act_type; p.ab_format = model->data_type == FMOE_DT_FP16 ? 0 : 1;
   p.elem_bytes = c->eb;
+  { const char* dbg = std::getenv("FMOE_DEBUG"); p.debug_flags = dbg ? std::atoi(dbg) : 0; }
   p.tiles_n0 = (I + g.tile_n0 - 1) / g.tile_n0;
   p.tiles_n1 = (H + g.tile_n1 - 1) / g.tile_n1;
   p.landing_rows = g.landing_rows; p.max_mtiles = max_mtiles;

@@ -19,9 +19,15 @@
 //    and waits on the task's readiness counters itself.  Tickets are handed out in an order
 //    in which a task only ever waits on tasks with smaller tickets, so the kernel cannot
 //    deadlock as long as all CTAs are co-resident (grid <= SM count, one CTA per SM).
-//  * Each CTA is warp-specialised: warp 0 = scheduler + TMA producer, warp 1 = UMMA issuer
-//    and TMEM owner, warps 2..5 = epilogue.  A 4-stage TMA->UMMA ring (48 KB per stage) and
-//    a double-buffered 2 x 256-column TMEM accumulator overlap loads, MMA and epilogue.
+//  * CTAs work in pairs (clusters of 2 on the two SMs of a TPC) on 256 x 256 output tiles with
+//    tcgen05.mma.cta_group::2: each CTA loads its own 128 rows of A and HALF of the B tile, so
+//    per SM the B bytes through shared memory are halved (the single-CTA form of this loop is
+//    bound by shared-memory bandwidth: TMA fill + UMMA operand reads).  Each CTA is
+//    warp-specialised: warp 0 = scheduler + TMA producer, warp 1 = UMMA issuer (leader CTA
+//    only) and TMEM owner, warps 2..5 = epilogue.  A 6-stage TMA->UMMA ring (32 KB per CTA per
+//    stage) and a double-buffered 2 x 256-column TMEM accumulator overlap loads, MMA and
+//    epilogue.  The leader's scheduler draws the ticket, waits for readiness and passes the
+//    ticket to the follower through distributed shared memory.
 //  * Gate and up projections are ONE UMMA of N = 256 (gate rows | up rows in the B tile);
 //    the SiLU-gate product is formed in the epilogue straight from TMEM.  The reference
 //    runs its main loop twice and parks the gate tile in shared memory
@@ -58,14 +64,18 @@ struct alignas(64) TmaMaps {
 
 enum : int { kTaskGemm0 = 0, kTaskGemm1 = 1, kTaskStop = 2 };
 
+// What one CTA of a pair does for one ticket: its own M tile (the leader takes the even tile of
+// the group, the follower the odd one) of the pair's 256 x 256 output tile.
 struct Task {
-  int kind, lx, mt, row0, rows, n, m_in_expert, pad;
+  int kind, lx, mt, row0, rows, n, m_in_expert, ticket;
 };
 
 struct Control {
   uint64_t full[kStages], empty[kStages];
   uint64_t acc_full[kAccBufs], acc_empty[kAccBufs];
   uint64_t task_full[kTaskSlots], task_empty[kTaskSlots];
+  uint64_t pair_full[kTaskSlots], pair_empty[kTaskSlots];   // leader -> follower ticket ring
+  uint32_t pair_ticket[kTaskSlots];
   Task tasks[kTaskSlots];
   uint32_t tmem_base;
   uint32_t ok;            // cleared when a CTA-wide wait failed
@@ -233,7 +243,7 @@ __host__ __device__ inline size_t tables_ints(int W, int E, int nLx) {
 }
 
 template <typename T>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
 moe_forward_kernel(const __grid_constant__ MoeParams p, const __grid_constant__ TmaMaps maps) {
   extern __shared__ uint8_t smem_raw[];
   // stage ring first, 1024-byte aligned (128-byte swizzle atoms)
@@ -256,6 +266,8 @@ moe_forward_kernel(const __grid_constant__ MoeParams p, const __grid_constant__ 
     tb.tot = q;
   }
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const uint32_t pair_rank = cluster_ctarank();   // 0 = leader of the CTA pair, 1 = follower
+  const bool leader = pair_rank == 0;
   const int W = p.W, E = p.E, nLx = p.nLx;
   char* const self = p.peers[p.rank];
   constexpr int EB = Elem<T>::kBytes;     // bytes per element of tokens, return rows and output
@@ -266,8 +278,13 @@ moe_forward_kernel(const __grid_constant__ MoeParams p, const __grid_constant__ 
   // ---- set-up: barriers, TMEM, epoch ---------------------------------------------------
   if (tid == 0) {
     for (int i = 0; i < kStages; ++i) { mbar_init(&ctl->full[i], 1); mbar_init(&ctl->empty[i], 1); }
-    for (int i = 0; i < kAccBufs; ++i) { mbar_init(&ctl->acc_full[i], 1); mbar_init(&ctl->acc_empty[i], 4); }
-    for (int i = 0; i < kTaskSlots; ++i) { mbar_init(&ctl->task_full[i], 1); mbar_init(&ctl->task_empty[i], 5); }
+    // acc_empty collects the four epilogue warps of BOTH CTAs of the pair (only the leader's is
+    // waited on); task_empty: this CTA's MMA thread (leader only) + its four epilogue warps
+    for (int i = 0; i < kAccBufs; ++i) { mbar_init(&ctl->acc_full[i], 1); mbar_init(&ctl->acc_empty[i], 8); }
+    for (int i = 0; i < kTaskSlots; ++i) {
+      mbar_init(&ctl->task_full[i], 1); mbar_init(&ctl->task_empty[i], leader ? 5 : 4);
+      mbar_init(&ctl->pair_full[i], 1); mbar_init(&ctl->pair_empty[i], 1);
+    }
     ctl->ok = 1;
     ctl->epoch = *p.epoch;
     mbar_fence_init();
@@ -275,11 +292,12 @@ moe_forward_kernel(const __grid_constant__ MoeParams p, const __grid_constant__ 
     prefetch_tmap(&maps.up_v); prefetch_tmap(&maps.down);
   }
   if (warp == 1) {
-    tmem_alloc(&ctl->tmem_base, 512);
-    tmem_relinquish();
+    tmem_alloc_pair(&ctl->tmem_base, 512);
+    tmem_relinquish_pair();
   }
   tc_fence_before_sync();
   __syncthreads();
+  cluster_sync_all();   // the peer's barriers exist before anything arrives on them
   tc_fence_after_sync();
   const uint64_t epoch = ctl->epoch;
   const uint64_t flag_val = epoch + 1;
@@ -368,18 +386,19 @@ moe_forward_kernel(const __grid_constant__ MoeParams p, const __grid_constant__ 
     // task order: GEMM1 of expert i trails GEMM0 of expert i by `lag` experts, the smallest lag
     // whose GEMM0 tiles cover two tickets per CTA, so that by the time a GEMM1 ticket is drawn the
     // GEMM0 tiles it depends on are long finished: G0(0..lag-1), G0(lag), G1(0), G0(lag+1), G1(1), ...
+    // A ticket is a group of two M tiles (one per CTA of a pair) times one N tile.
     int lag = 1;
     while (lag < nLx && tb.lx_mt0[lag] * p.tiles_n0 < 2 * static_cast<int>(gridDim.x)) ++lag;
     int ns = 0, first = 0;
     for (int i = 0; i < nLx + lag; ++i) {
       if (i < nLx) {
         tb.seg_first[ns] = first; tb.seg_kind[ns] = kTaskGemm0; tb.seg_lx[ns] = i; ++ns;
-        first += (tb.lx_mt0[i + 1] - tb.lx_mt0[i]) * p.tiles_n0;
+        first += (tb.lx_mt0[i + 1] - tb.lx_mt0[i] + 1) / 2 * p.tiles_n0;
       }
       if (i >= lag) {
         const int j = i - lag;
         tb.seg_first[ns] = first; tb.seg_kind[ns] = kTaskGemm1; tb.seg_lx[ns] = j; ++ns;
-        first += (tb.lx_mt0[j + 1] - tb.lx_mt0[j]) * p.tiles_n1;
+        first += (tb.lx_mt0[j + 1] - tb.lx_mt0[j] + 1) / 2 * p.tiles_n1;
       }
     }
     tb.seg_first[ns] = first;
@@ -453,109 +472,150 @@ moe_forward_kernel(const __grid_constant__ MoeParams p, const __grid_constant__ 
   }
 
   // ---- expert GEMMs ---------------------------------------------------------------------
+  // Two CTAs (a cluster of 2, on the two SMs of one TPC) work on one 256 x 256 output tile:
+  // each loads its own 128 rows of A and its own half of the B tile, the leader issues
+  // tcgen05.mma.cta_group::2, each keeps its 128 rows of the accumulator in its own TMEM.  Per
+  // SM that halves the B bytes written to and read from shared memory per flop, which is what
+  // bounds the single-CTA form of this loop.
   const int nk0 = p.H / kTileK, nk1 = p.I / kTileK;
   // plane pairs (A plane, B plane) per K block, smallest contributions first
   constexpr int kPairs = kPlanes == 1 ? 1 : 6;
   constexpr int kBufs = kPlanes == 1 ? kAccBufs : 1;   // fp32 layers use both TMEM halves per task
   constexpr int kPairA[6] = {0, 2, 1, 0, 1, 0};
   constexpr int kPairB[6] = {2, 0, 1, 1, 0, 0};
+  // ticket -> this CTA's task
+  auto decode = [&](int ticket) -> Task {
+    Task t{};
+    t.ticket = ticket;
+    if (ticket >= ctl->total_tasks) { t.kind = kTaskStop; return t; }
+    int lo = 0, hi = ctl->n_segs;
+    while (hi - lo > 1) {
+      const int mid = (lo + hi) >> 1;
+      if (tb.seg_first[mid] <= ticket) lo = mid; else hi = mid;
+    }
+    const int lx = tb.seg_lx[lo];
+    const int idx = ticket - tb.seg_first[lo];
+    const int mts = tb.lx_mt0[lx + 1] - tb.lx_mt0[lx];
+    const int groups = (mts + 1) / 2;
+    t.kind = tb.seg_kind[lo];
+    t.lx = lx;
+    t.n = idx / groups;
+    t.m_in_expert = 2 * (idx - t.n * groups) + static_cast<int>(pair_rank);
+    t.mt = tb.lx_mt0[lx] + t.m_in_expert;
+    t.row0 = tb.lx_base[lx] + t.m_in_expert * kTileM;
+    t.rows = max(0, min(kTileM, tb.lx_rows[lx] - t.m_in_expert * kTileM));   // 0: no such M tile
+    return t;
+  };
+
   if (ctl->ok && warp == 0) {
     if (lane == 0) {
-      // scheduler + TMA producer
+      // scheduler (leader: draws tickets and waits for readiness) + TMA producer (both CTAs)
       uint32_t fill = 0;  // stage fills issued so far
       uint32_t tslot = 0;
       bool ok = true;
       for (uint32_t it = 0; ok; ++it, tslot = (tslot + 1) % kTaskSlots) {
-        const int ticket = static_cast<int>(atomicAdd(p.ticket, 1u));
-        Task t{};
-        if (ticket >= ctl->total_tasks) {
-          t.kind = kTaskStop;
+        const uint32_t ring_par = (it / kTaskSlots) & 1;
+        int ticket;
+        if (leader) {
+          ticket = static_cast<int>(atomicAdd(p.ticket, 1u));
         } else {
-          int lo = 0, hi = ctl->n_segs;
-          while (hi - lo > 1) {
-            const int mid = (lo + hi) >> 1;
-            if (tb.seg_first[mid] <= ticket) lo = mid; else hi = mid;
+          if (!mbar_wait_cluster(&ctl->pair_full[tslot], ring_par, p.abort_word)) {
+            fail(p, FMOE_PHASE_TASK, -3); ok = false; break;
           }
-          const int lx = tb.seg_lx[lo];
-          const int idx = ticket - tb.seg_first[lo];
-          const int mts = tb.lx_mt0[lx + 1] - tb.lx_mt0[lx];
-          t.kind = tb.seg_kind[lo];
-          t.lx = lx;
-          t.n = idx / mts;
-          t.m_in_expert = idx - t.n * mts;
-          t.mt = tb.lx_mt0[lx] + t.m_in_expert;
-          t.row0 = tb.lx_base[lx] + t.m_in_expert * kTileM;
-          t.rows = min(kTileM, tb.lx_rows[lx] - t.m_in_expert * kTileM);
+          ticket = static_cast<int>(ctl->pair_ticket[tslot]);
+          mbar_arrive_cluster(map_to_cta(&ctl->pair_empty[tslot], 0));
         }
-        if (!mbar_wait(&ctl->task_empty[tslot], ((it / kTaskSlots) & 1) ^ 1, p.abort_word)) {
+        const Task t = decode(ticket);
+        if (leader) {
+          // readiness of BOTH M tiles of the group, then hand the ticket to the follower
+          if (t.kind == kTaskGemm0) {
+            const int e = p.local_e[p.rank * nLx + t.lx];
+            const uint32_t* arrived = reinterpret_cast<const uint32_t*>(self + p.lay.disp_arrived);
+            const int lo_row = t.m_in_expert * kTileM, hi_row = lo_row + 2 * kTileM;
+            int off = 0;
+            for (int s = 0; s < W && ok; ++s) {
+              const int ns = tb.n[s * E + e];
+              if (ns > 0 && off < hi_row && off + ns > lo_row) {
+                if (!wait_counter_sys(arrived + s * nLx + t.lx, static_cast<uint32_t>(ns), p)) {
+                  fail(p, FMOE_PHASE_DISPATCH_ARRIVAL, s); ok = false;
+                }
+              }
+              off += ns;
+            }
+          } else if (t.kind == kTaskGemm1) {
+            const int mts = tb.lx_mt0[t.lx + 1] - tb.lx_mt0[t.lx];
+            for (int q = 0; q < 2 && ok; ++q) {
+              if (t.m_in_expert + q >= mts) break;
+              if (!wait_counter_gpu(p.gemm0_done + t.mt + q, static_cast<uint32_t>(4 * p.tiles_n0), p)) {
+                fail(p, FMOE_PHASE_GEMM0_DONE, t.mt + q); ok = false;
+              }
+            }
+          }
+          if (!ok) break;
+          if (!mbar_wait_cluster(&ctl->pair_empty[tslot], ring_par ^ 1, p.abort_word)) {
+            fail(p, FMOE_PHASE_TASK, -4); ok = false; break;
+          }
+          st_cluster_u32(map_to_cta(&ctl->pair_ticket[tslot], 1), static_cast<uint32_t>(ticket));
+          mbar_arrive_cluster(map_to_cta(&ctl->pair_full[tslot], 1));
+        }
+        if (!mbar_wait(&ctl->task_empty[tslot], ring_par ^ 1, p.abort_word)) {
           fail(p, FMOE_PHASE_TASK, ticket); ok = false; break;
         }
         ctl->tasks[tslot] = t;
         mbar_arrive(&ctl->task_full[tslot]);
         if (t.kind == kTaskStop) break;
-
-        // readiness
-        if (t.kind == kTaskGemm0) {
-          const int e = p.local_e[p.rank * nLx + t.lx];
-          const uint32_t* arrived = reinterpret_cast<const uint32_t*>(self + p.lay.disp_arrived);
-          const int lo_row = t.m_in_expert * kTileM, hi_row = lo_row + t.rows;
-          int off = 0;
-          for (int s = 0; s < W && ok; ++s) {
-            const int ns = tb.n[s * E + e];
-            if (ns > 0 && off < hi_row && off + ns > lo_row) {
-              if (!wait_counter_sys(arrived + s * nLx + t.lx, static_cast<uint32_t>(ns), p)) {
-                fail(p, FMOE_PHASE_DISPATCH_ARRIVAL, s); ok = false;
-              }
-            }
-            off += ns;
-          }
-        } else {
-          if (!wait_counter_gpu(p.gemm0_done + t.mt, static_cast<uint32_t>(4 * p.tiles_n0), p)) {
-            fail(p, FMOE_PHASE_GEMM0_DONE, t.mt); ok = false;
-          }
-        }
-        if (!ok) break;
         fence_proxy_async();
 
         const bool g0 = t.kind == kTaskGemm0;
         const int nk = g0 ? nk0 : nk1;
         const CUtensorMap* map_a = g0 ? &maps.landing : &maps.y;
-        const CUtensorMap* map_b0 = g0 ? &maps.up : &maps.down;
-        const CUtensorMap* map_b1 = g0 ? (p.gated ? &maps.up_v : &maps.up) : &maps.down;
-        int brow0, brow1;
+        // this CTA's half of the B tile: GEMM0 gated = gate rows (leader) | up rows (follower)
+        const CUtensorMap* map_b;
+        int brow;
         if (g0) {
-          if (p.gated) { brow0 = t.lx * p.I + t.n * 128; brow1 = brow0; }
-          else { brow0 = t.lx * p.I + t.n * 256; brow1 = brow0 + 128; }
+          if (p.gated) { map_b = leader ? &maps.up : &maps.up_v; brow = t.lx * p.I + t.n * 128; }
+          else { map_b = &maps.up; brow = t.lx * p.I + t.n * 256 + static_cast<int>(pair_rank) * 128; }
         } else {
-          brow0 = t.lx * p.H + t.n * 256; brow1 = brow0 + 128;
+          map_b = &maps.down; brow = t.lx * p.H + t.n * 256 + static_cast<int>(pair_rank) * 128;
         }
         const int b_plane_rows = g0 ? nLx * p.I : nLx * p.H;   // rows of one BF16 plane of the weights
         for (int kb = 0; kb < nk && ok; ++kb) {
           for (int pp = 0; pp < kPairs; ++pp, ++fill) {
             const int pa = kPlanes == 1 ? 0 : kPairA[pp], pb = kPlanes == 1 ? 0 : kPairB[pp];
             const uint32_t s = fill % kStages;
-            if (!mbar_wait(&ctl->empty[s], ((fill / kStages) & 1) ^ 1, p.abort_word)) {
+            if (!mbar_wait_cluster(&ctl->empty[s], ((fill / kStages) & 1) ^ 1, p.abort_word)) {
               fail(p, FMOE_PHASE_PIPE_EMPTY, ticket); ok = false; break;
             }
             uint8_t* sa = stages + s * kStageBytes;
             uint8_t* sb = sa + kStageABytes;
-            mbar_expect_tx(&ctl->full[s], kStageBytes);
-            tma_load_2d(sa, map_a, &ctl->full[s], kb * kTileK, t.row0 + pa * p.landing_rows);
-            tma_load_2d(sb, map_b0, &ctl->full[s], kb * kTileK, brow0 + pb * b_plane_rows);
-            tma_load_2d(sb + kStageBBytes / 2, map_b1, &ctl->full[s], kb * kTileK, brow1 + pb * b_plane_rows);
+            if (p.debug_flags & 2) {   // timing experiment: no loads, the MMAs chew on stale tiles
+              if (leader) mbar_arrive(&ctl->full[s]);
+              continue;
+            }
+            // the leader's barrier counts the bytes of both CTAs
+            if (leader) mbar_expect_tx(&ctl->full[s], 2 * kStageBytes);
+            tma_load_2d_pair(sa, map_a, &ctl->full[s], kb * kTileK, t.row0 + pa * p.landing_rows);
+            tma_load_2d_pair(sb, map_b, &ctl->full[s], kb * kTileK, brow + pb * b_plane_rows);
           }
         }
       }
       if (!ok) {
-        // let the copies already in flight land before this CTA's shared memory goes away
-        const uint32_t first = fill > kStages ? fill - kStages : 0;
-        for (uint32_t f = first; f < fill; ++f)
-          mbar_wait(&ctl->full[f % kStages], (f / kStages) & 1, nullptr);
+        // let the copies already in flight land before this CTA's shared memory goes away: the
+        // leader can watch its barriers (bounded), the follower allows the same time to pass
+        const long long t_start = clock_now();
+        if (leader) {
+          const uint32_t first = fill > kStages ? fill - kStages : 0;
+          for (uint32_t f = first; f < fill; ++f)
+            while (!mbar_try_wait_cluster(&ctl->full[f % kStages], (f / kStages) & 1) &&
+                   clock_now() - t_start < 2000000LL) {}
+        } else {
+          while (clock_now() - t_start < 2000000LL) {}
+        }
       }
     }
   } else if (ctl->ok && warp == 1) {
-    if (lane == 0) {
-      const uint32_t idesc = umma_idesc_f16(Cvt<T>::kFormat, kTileM, kUmmaN);
+    if (lane == 0 && leader) {
+      const uint32_t idesc = umma_idesc_f16(Cvt<T>::kFormat, 2 * kTileM, kUmmaN);
       uint32_t fill = 0, tslot = 0, acc_it = 0;
       for (uint32_t it = 0;; ++it, tslot = (tslot + 1) % kTaskSlots) {
         if (!mbar_wait(&ctl->task_full[tslot], (it / kTaskSlots) & 1, p.abort_word)) {
@@ -566,7 +626,7 @@ moe_forward_kernel(const __grid_constant__ MoeParams p, const __grid_constant__ 
         if (t.kind == kTaskStop) break;
         const int nk = (t.kind == kTaskGemm0 ? nk0 : nk1) * kPairs;
         const uint32_t buf = acc_it % kBufs;
-        if (!mbar_wait(&ctl->acc_empty[buf], ((acc_it / kBufs) & 1) ^ 1, p.abort_word)) {
+        if (!mbar_wait_cluster(&ctl->acc_empty[buf], ((acc_it / kBufs) & 1) ^ 1, p.abort_word)) {
           fail(p, FMOE_PHASE_TMEM_EMPTY, t.mt); break;
         }
         tc_fence_after_sync();
@@ -575,7 +635,7 @@ moe_forward_kernel(const __grid_constant__ MoeParams p, const __grid_constant__ 
         bool ok = true;
         for (int kb = 0; kb < nk; ++kb, ++fill) {
           const uint32_t s = fill % kStages;
-          if (!mbar_wait(&ctl->full[s], (fill / kStages) & 1, p.abort_word)) {
+          if (!mbar_wait_cluster(&ctl->full[s], (fill / kStages) & 1, p.abort_word)) {
             fail(p, FMOE_PHASE_PIPE_FULL, t.mt); ok = false; break;
           }
           tc_fence_after_sync();
@@ -585,22 +645,25 @@ moe_forward_kernel(const __grid_constant__ MoeParams p, const __grid_constant__ 
           const bool lead = kPlanes == 1 || (kb % kPairs) == kPairs - 1;
           const uint32_t d = lead ? d_tmem : d_corr;
           const bool first = lead ? (kb < kPairs) : (kb == 0);
+          if (!(p.debug_flags & 1)) {   // flag 1 = timing experiment: loads only, no MMAs
 #pragma unroll
-          for (int k = 0; k < kTileK / 16; ++k) {
-            umma_f16(d, umma_desc_sw128(a_addr + k * 32), umma_desc_sw128(b_addr + k * 32),
-                     idesc, (!first || k > 0) ? 1u : 0u);
+            for (int k = 0; k < kTileK / 16; ++k) {
+              umma_f16_pair(d, umma_desc_sw128(a_addr + k * 32), umma_desc_sw128(b_addr + k * 32),
+                            idesc, (!first || k > 0) ? 1u : 0u);
+            }
           }
-          umma_commit(&ctl->empty[s]);
+          umma_commit_pair(&ctl->empty[s], 3);    // frees the stage in both CTAs
         }
         if (!ok) break;
-        umma_commit(&ctl->acc_full[buf]);
+        umma_commit_pair(&ctl->acc_full[buf], 3); // both CTAs' epilogues may read their rows
         ++acc_it;
       }
     }
   } else if (ctl->ok) {
-    // epilogue warps: TMEM lane quadrant = warp id mod 4
+    // epilogue warps: TMEM lane quadrant = warp id mod 4; this CTA's 128 rows of the pair's tile
     const int quad = warp & 3;
     const int row_in_tile = quad * 32 + lane;
+    const uint32_t acc_empty_leader = map_to_cta(&ctl->acc_empty[0], 0);
     uint32_t tslot = 0, acc_it = 0;
     for (uint32_t it = 0;; ++it, tslot = (tslot + 1) % kTaskSlots) {
       if (!mbar_wait(&ctl->task_full[tslot], (it / kTaskSlots) & 1, p.abort_word)) {
@@ -611,13 +674,20 @@ moe_forward_kernel(const __grid_constant__ MoeParams p, const __grid_constant__ 
       if (lane == 0) mbar_arrive(&ctl->task_empty[tslot]);
       if (t.kind == kTaskStop) break;
       const uint32_t buf = acc_it % kBufs;
-      if (!mbar_wait(&ctl->acc_full[buf], (acc_it / kBufs) & 1, p.abort_word)) {
+      if (!mbar_wait_cluster(&ctl->acc_full[buf], (acc_it / kBufs) & 1, p.abort_word)) {
         fail(p, FMOE_PHASE_TMEM_FULL, t.mt); break;
       }
       tc_fence_after_sync();
       const uint32_t taddr = ctl->tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + buf * kUmmaN;
       const bool valid = row_in_tile < t.rows;
       const int row = t.row0 + row_in_tile;
+      // hands this warp's quarter of the accumulator back to the leader's MMA thread; called right
+      // after the last TMEM load of the task, before the remaining math and stores
+      auto release_acc = [&]() {
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(acc_empty_leader + buf * static_cast<uint32_t>(sizeof(uint64_t)));
+      };
 
       if (t.kind == kTaskGemm0) {
         char* yrow = static_cast<char*>(p.y) + static_cast<size_t>(row) * p.I * 2;
@@ -641,6 +711,7 @@ moe_forward_kernel(const __grid_constant__ MoeParams p, const __grid_constant__ 
                 u[i] = __float_as_uint(__uint_as_float(u[i]) + __uint_as_float(cu[i]));
               }
             }
+            if (c == 3) release_acc();
             const int col0 = col_base + c * 32;
             if (valid && col0 < p.I) {
               float y[32];
@@ -670,6 +741,7 @@ moe_forward_kernel(const __grid_constant__ MoeParams p, const __grid_constant__ 
 #pragma unroll
               for (int i = 0; i < 32; ++i) a[i] = __float_as_uint(__uint_as_float(a[i]) + __uint_as_float(ca[i]));
             }
+            if (c == 7) release_acc();
             const int col0 = col_base + c * 32;
             if (valid && col0 < p.I) {
               float y[32];
@@ -682,13 +754,9 @@ moe_forward_kernel(const __grid_constant__ MoeParams p, const __grid_constant__ 
             }
           }
         }
-        tc_fence_before_sync();
-        __threadfence();
+        // every lane's stores happen before the barrier, the barrier before lane 0's release
         __syncwarp();
-        if (lane == 0) {
-          mbar_arrive(&ctl->acc_empty[buf]);
-          red_add_release_gpu(p.gemm0_done + t.mt, 1u);
-        }
+        if (lane == 0 && t.rows > 0) red_add_release_gpu(p.gemm0_done + t.mt, 1u);
       } else {
         uint32_t meta = 0;
         if (valid) meta = __ldcg(reinterpret_cast<const uint32_t*>(self + p.lay.landing_meta) + row);
@@ -709,6 +777,7 @@ moe_forward_kernel(const __grid_constant__ MoeParams p, const __grid_constant__ 
 #pragma unroll
             for (int i = 0; i < 32; ++i) a[i] = __float_as_uint(__uint_as_float(a[i]) + __uint_as_float(ca[i]));
           }
+          if (c == 7) release_acc();
           const int col0 = col_base + c * 32;
           if (valid && col0 < p.H) {
             float o[32];
@@ -718,10 +787,7 @@ moe_forward_kernel(const __grid_constant__ MoeParams p, const __grid_constant__ 
             store_result32<T>(orow, col0, o);
           }
         }
-        tc_fence_before_sync();
-        __threadfence_system();
         __syncwarp();
-        if (lane == 0) mbar_arrive(&ctl->acc_empty[buf]);
         // tell every owner how many of its rows this warp just delivered
         for (int s = 0; s < W; ++s) {
           const unsigned b = __ballot_sync(0xffffffffu, valid && src == s);
@@ -795,8 +861,11 @@ moe_forward_kernel(const __grid_constant__ MoeParams p, const __grid_constant__ 
   }
 
   // ---- leave ------------------------------------------------------------------------------
+  tc_fence_before_sync();
   __syncthreads();
-  if (warp == 1) tmem_dealloc(ctl->tmem_base, 512);
+  cluster_sync_all();   // the peer no longer touches this CTA's barriers, tiles or TMEM
+  tc_fence_after_sync();
+  if (warp == 1) tmem_dealloc_pair(ctl->tmem_base, 512);
   if (tid == 0) {
     __threadfence();
     const uint32_t prev = atomicAdd(p.done_ctas, 1u);

@@ -23,7 +23,8 @@ class RankLayout:
     lx_base: List[int]         # [nLx] first landing row of local expert lx (multiple of 128)
     lx_rows: List[int]         # [nLx] rows of local expert lx over all sources
     mtile0: List[int]          # [nLx+1] prefix of M tiles
-    tasks: List[tuple]         # (kind, lx, m, n) in ticket order; kind 0 = GEMM0, 1 = GEMM1
+    tasks: List[tuple]         # (kind, lx, group, n) in ticket order; kind 0 = GEMM0, 1 = GEMM1;
+                               # a group is two consecutive M tiles, one per CTA of a pair
 
 
 def build(counts: Sequence[Sequence[int]], rank: int, expert_map: Sequence[int], ec: int,
@@ -54,12 +55,12 @@ def build(counts: Sequence[Sequence[int]], rank: int, expert_map: Sequence[int],
     tasks = []
     for i in range(nlx + lag):
         if i < nlx:
-            mts = mtile0[i + 1] - mtile0[i]
-            tasks += [(0, i, m, n) for n in range(tiles_n0) for m in range(mts)]
+            groups = (mtile0[i + 1] - mtile0[i] + 1) // 2
+            tasks += [(0, i, g, n) for n in range(tiles_n0) for g in range(groups)]
         if i >= lag:
             j = i - lag
-            mts = mtile0[j + 1] - mtile0[j]
-            tasks += [(1, j, m, n) for n in range(tiles_n1) for m in range(mts)]
+            groups = (mtile0[j + 1] - mtile0[j] + 1) // 2
+            tasks += [(1, j, g, n) for n in range(tiles_n1) for g in range(groups)]
     return RankLayout(sent, dst_row0, lx_base, lx_rows, mtile0, tasks)
 
 

@@ -49,11 +49,11 @@ def _rank_main(rank, world, port, name, q):
         assert lay.lx_base[-1] + -(-lay.lx_rows[-1] // 128) * 128 <= cap
         # every GEMM1 task comes after all GEMM0 tasks of its M tile (deadlock freedom of the order)
         seen = set()
-        for kind, lx, m, n in lay.tasks:
+        for kind, lx, grp, n in lay.tasks:
             if kind == 0:
-                seen.add((lx, m, n))
+                seen.add((lx, grp, n))
             else:
-                assert all((lx, m, n0) in seen for n0 in range(3))
+                assert all((lx, grp, n0) in seen for n0 in range(3))
 
         # dispatch: (dst rank) -> list of (landing row, meta, row)
         outbox = [[] for _ in range(world)]
@@ -130,7 +130,8 @@ def test_layout_matches_hand_computed_example():
     assert lay.lx_base == [0, 128] and lay.lx_rows == [128, 129]
     assert lay.mtile0 == [0, 1, 3]
     kinds = [(t[0], t[1]) for t in lay.tasks]
-    assert kinds == [(0, 0)] * 2 + [(0, 1)] * 4 + [(1, 0)] * 1 + [(1, 1)] * 2
+    # expert 0: one M tile, expert 1: two M tiles = one group (a CTA pair takes both)
+    assert kinds == [(0, 0)] * 2 + [(0, 1)] * 2 + [(1, 0)] * 1 + [(1, 1)] * 1
     # a wider grid makes GEMM1 trail by more experts: all GEMM0 tiles first here
     wide = layout.build(counts, 1, [0, 0, 1, 1], ec=128, tiles_n0=2, tiles_n1=1, grid=148)
-    assert [(t[0], t[1]) for t in wide.tasks] == [(0, 0)] * 2 + [(0, 1)] * 4 + [(1, 0)] * 1 + [(1, 1)] * 2
+    assert [(t[0], t[1]) for t in wide.tasks] == kinds
