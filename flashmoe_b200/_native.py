@@ -54,7 +54,8 @@ class Status(C.Structure):
 class Geometry(C.Structure):
     _fields_ = [(n, C.c_int32) for n in (
         "tile_m", "tile_n0", "tile_n1", "tile_k", "stages", "round_ec", "landing_rows", "grid",
-        "threads", "smem_bytes")] + [("symm_bytes", C.c_int64), ("workspace_bytes", C.c_int64)]
+        "threads", "smem_bytes", "cta_pairs", "reserved")] + [("symm_bytes", C.c_int64),
+                                                               ("workspace_bytes", C.c_int64)]
 
 
 # name -> (restype, argtypes); the single source of truth for the symbol-export test too

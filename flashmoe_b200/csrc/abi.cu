@@ -229,7 +229,7 @@ int fmoe_ctx_create(const fmoe_model_desc* model, const fmoe_ep_desc* ep, void* 
   const int EC = model->expert_peer_capacity;
   const bool gated = model->mlp_type == FMOE_MLP_GATED;
   fmoe_geometry& g = c->geo;
-  g.tile_m = kTileM; g.tile_k = kTileK; g.stages = kStages;
+  g.tile_m = kTileM; g.tile_k = kTileK;
   g.tile_n0 = gated ? 128 : 256; g.tile_n1 = 256;
   g.round_ec = static_cast<int>(align_up(EC, kTileM));
   const long long cap_a = static_cast<long long>(nLx) * align_up(static_cast<size_t>(W) * EC, kTileM);
@@ -291,6 +291,15 @@ int fmoe_ctx_create(const fmoe_model_desc* model, const fmoe_ep_desc* ep, void* 
   p.gated = gated ? 1 : 0; p.act = model->act_type; p.ab_format = model->data_type == FMOE_DT_FP16 ? 0 : 1;
   p.elem_bytes = c->eb;
   { const char* dbg = std::getenv("FMOE_DEBUG"); p.debug_flags = dbg ? std::atoi(dbg) : 0; }
+  // CTA pairs pay off when experts hold several M tiles; with <= ~1 tile per expert a lone CTA per
+  // tile keeps more weight bytes in flight.  Expected rows per expert if routing is balanced:
+  {
+    const double rows_per_expert = static_cast<double>(W) * S * k / E;
+    p.pair = rows_per_expert >= 192.0 ? 1 : 0;
+    const char* force = std::getenv("FMOE_PAIR");
+    if (force) p.pair = std::atoi(force) ? 1 : 0;
+    g.cta_pairs = p.pair; g.stages = p.pair ? 6 : 4;
+  }
   p.tiles_n0 = (I + g.tile_n0 - 1) / g.tile_n0;
   p.tiles_n1 = (H + g.tile_n1 - 1) / g.tile_n1;
   p.landing_rows = g.landing_rows; p.max_mtiles = max_mtiles;

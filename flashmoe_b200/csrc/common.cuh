@@ -28,13 +28,11 @@ struct __align__(16) Route {
 constexpr int kTileM = 128;      // rows of an expert's batch per CTA (a CTA pair covers 256)
 constexpr int kTileK = 64;       // 64 x 16-bit = one 128-byte swizzle span
 constexpr int kUmmaN = 256;      // UMMA N: gate|up halves for GEMM0, 256 output columns for GEMM1
-constexpr int kStages = 6;       // TMA -> UMMA ring depth
+// TMA -> UMMA ring: 6 stages of 32 KB per CTA in pair mode, 4 stages of 48 KB alone (192 KB both)
 constexpr int kAccBufs = 2;      // TMEM accumulator double buffer (2 x 256 columns)
 constexpr int kTaskSlots = 4;    // task ring between the scheduler warp and its consumers
 constexpr int kThreads = 192;    // warp 0 scheduler + TMA, warp 1 UMMA, warps 2..5 epilogue
-constexpr uint32_t kStageABytes = kTileM * kTileK * 2;        // this CTA's 128 rows of A
-constexpr uint32_t kStageBBytes = (kUmmaN / 2) * kTileK * 2;  // this CTA's half of the B tile
-constexpr uint32_t kStageBytes = kStageABytes + kStageBBytes; // 32 KB per CTA per stage
+constexpr uint32_t kStageABytes = kTileM * kTileK * 2;        // 128 rows x 64 columns of 16-bit: 16 KB
 
 constexpr uint32_t kMetaSrcShift = 26;  // landing meta = (source rank << 26) | return row
 
@@ -56,6 +54,7 @@ struct MoeParams {
   int W, rank, nLx;
   int gated, act, ab_format;  // ab_format: 0 fp16, 1 bf16 (fp32 layers run as BF16 planes)
   int elem_bytes;             // 2, or 4 for fp32 layers
+  int pair;                   // 1: CTA pairs (cta_group::2), 0: every CTA alone
   int debug_flags;            // FMOE_DEBUG (environment, read at create): 1 = skip MMAs, 2 = skip loads (timing experiments; results are garbage)
   int tiles_n0, tiles_n1;
   int landing_rows;

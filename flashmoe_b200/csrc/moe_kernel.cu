@@ -71,7 +71,7 @@ struct Task {
 };
 
 struct Control {
-  uint64_t full[kStages], empty[kStages];
+  uint64_t full[6], empty[6];   // ring depth: 6 in pair mode, 4 alone
   uint64_t acc_full[kAccBufs], acc_empty[kAccBufs];
   uint64_t task_full[kTaskSlots], task_empty[kTaskSlots];
   uint64_t pair_full[kTaskSlots], pair_empty[kTaskSlots];   // leader -> follower ticket ring
@@ -242,14 +242,22 @@ __host__ __device__ inline size_t tables_ints(int W, int E, int nLx) {
          2 * nLx + 2 * nLx + E;
 }
 
-template <typename T>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
-moe_forward_kernel(const __grid_constant__ MoeParams p, const __grid_constant__ TmaMaps maps) {
+// kPair = true: CTA pairs on 256-row tile groups (experts with several M tiles; tensor-bound work).
+// kPair = false: every CTA on its own 128 x 256 tile with the whole B tile (4 stages of 48 KB):
+// more weight bytes in flight per SM, which is what counts when experts hold <= 128 rows and the
+// layer streams weights from HBM.
+template <typename T, bool kPair>
+__device__ __forceinline__ void moe_forward_body(const MoeParams& p, const TmaMaps& maps) {
   extern __shared__ uint8_t smem_raw[];
+  constexpr int NS = kPair ? 6 : 4;                                   // ring depth
+  constexpr uint32_t SA = kStageABytes;                               // A tile of this CTA
+  constexpr uint32_t SB = kPair ? kStageABytes : 2 * kStageABytes;    // B rows this CTA loads
+  constexpr uint32_t STAGE = SA + SB;
+  constexpr int kGroup = kPair ? 2 : 1;                               // M tiles per ticket
   // stage ring first, 1024-byte aligned (128-byte swizzle atoms)
   uint8_t* stages = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                                ~static_cast<uintptr_t>(1023));
-  Control* ctl = reinterpret_cast<Control*>(stages + kStages * kStageBytes);
+  Control* ctl = reinterpret_cast<Control*>(stages + NS * STAGE);
   int* tab = reinterpret_cast<int*>(ctl + 1);
   Tables tb;
   {
@@ -266,7 +274,8 @@ moe_forward_kernel(const __grid_constant__ MoeParams p, const __grid_constant__ 
     tb.tot = q;
   }
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const uint32_t pair_rank = cluster_ctarank();   // 0 = leader of the CTA pair, 1 = follower
+  uint32_t pair_rank = 0;                         // 0 = leader of the CTA pair, 1 = follower
+  if constexpr (kPair) pair_rank = cluster_ctarank();
   const bool leader = pair_rank == 0;
   const int W = p.W, E = p.E, nLx = p.nLx;
   char* const self = p.peers[p.rank];
@@ -277,10 +286,10 @@ moe_forward_kernel(const __grid_constant__ MoeParams p, const __grid_constant__ 
 
   // ---- set-up: barriers, TMEM, epoch ---------------------------------------------------
   if (tid == 0) {
-    for (int i = 0; i < kStages; ++i) { mbar_init(&ctl->full[i], 1); mbar_init(&ctl->empty[i], 1); }
+    for (int i = 0; i < NS; ++i) { mbar_init(&ctl->full[i], 1); mbar_init(&ctl->empty[i], 1); }
     // acc_empty collects the four epilogue warps of BOTH CTAs of the pair (only the leader's is
     // waited on); task_empty: this CTA's MMA thread (leader only) + its four epilogue warps
-    for (int i = 0; i < kAccBufs; ++i) { mbar_init(&ctl->acc_full[i], 1); mbar_init(&ctl->acc_empty[i], 8); }
+    for (int i = 0; i < kAccBufs; ++i) { mbar_init(&ctl->acc_full[i], 1); mbar_init(&ctl->acc_empty[i], kPair ? 8 : 4); }
     for (int i = 0; i < kTaskSlots; ++i) {
       mbar_init(&ctl->task_full[i], 1); mbar_init(&ctl->task_empty[i], leader ? 5 : 4);
       mbar_init(&ctl->pair_full[i], 1); mbar_init(&ctl->pair_empty[i], 1);
@@ -292,12 +301,12 @@ moe_forward_kernel(const __grid_constant__ MoeParams p, const __grid_constant__ 
     prefetch_tmap(&maps.up_v); prefetch_tmap(&maps.down);
   }
   if (warp == 1) {
-    tmem_alloc_pair(&ctl->tmem_base, 512);
-    tmem_relinquish_pair();
+    if constexpr (kPair) { tmem_alloc_pair(&ctl->tmem_base, 512); tmem_relinquish_pair(); }
+    else { tmem_alloc(&ctl->tmem_base, 512); tmem_relinquish(); }
   }
   tc_fence_before_sync();
   __syncthreads();
-  cluster_sync_all();   // the peer's barriers exist before anything arrives on them
+  if constexpr (kPair) cluster_sync_all();   // the peer's barriers exist before anything arrives on them
   tc_fence_after_sync();
   const uint64_t epoch = ctl->epoch;
   const uint64_t flag_val = epoch + 1;
@@ -386,19 +395,19 @@ moe_forward_kernel(const __grid_constant__ MoeParams p, const __grid_constant__ 
     // task order: GEMM1 of expert i trails GEMM0 of expert i by `lag` experts, the smallest lag
     // whose GEMM0 tiles cover two tickets per CTA, so that by the time a GEMM1 ticket is drawn the
     // GEMM0 tiles it depends on are long finished: G0(0..lag-1), G0(lag), G1(0), G0(lag+1), G1(1), ...
-    // A ticket is a group of two M tiles (one per CTA of a pair) times one N tile.
+    // A ticket is a group of kGroup M tiles (one per CTA of a pair) times one N tile.
     int lag = 1;
     while (lag < nLx && tb.lx_mt0[lag] * p.tiles_n0 < 2 * static_cast<int>(gridDim.x)) ++lag;
     int ns = 0, first = 0;
     for (int i = 0; i < nLx + lag; ++i) {
       if (i < nLx) {
         tb.seg_first[ns] = first; tb.seg_kind[ns] = kTaskGemm0; tb.seg_lx[ns] = i; ++ns;
-        first += (tb.lx_mt0[i + 1] - tb.lx_mt0[i] + 1) / 2 * p.tiles_n0;
+        first += (tb.lx_mt0[i + 1] - tb.lx_mt0[i] + kGroup - 1) / kGroup * p.tiles_n0;
       }
       if (i >= lag) {
         const int j = i - lag;
         tb.seg_first[ns] = first; tb.seg_kind[ns] = kTaskGemm1; tb.seg_lx[ns] = j; ++ns;
-        first += (tb.lx_mt0[j + 1] - tb.lx_mt0[j] + 1) / 2 * p.tiles_n1;
+        first += (tb.lx_mt0[j + 1] - tb.lx_mt0[j] + kGroup - 1) / kGroup * p.tiles_n1;
       }
     }
     tb.seg_first[ns] = first;
@@ -496,11 +505,11 @@ moe_forward_kernel(const __grid_constant__ MoeParams p, const __grid_constant__ 
     const int lx = tb.seg_lx[lo];
     const int idx = ticket - tb.seg_first[lo];
     const int mts = tb.lx_mt0[lx + 1] - tb.lx_mt0[lx];
-    const int groups = (mts + 1) / 2;
+    const int groups = (mts + kGroup - 1) / kGroup;
     t.kind = tb.seg_kind[lo];
     t.lx = lx;
     t.n = idx / groups;
-    t.m_in_expert = 2 * (idx - t.n * groups) + static_cast<int>(pair_rank);
+    t.m_in_expert = kGroup * (idx - t.n * groups) + static_cast<int>(pair_rank);
     t.mt = tb.lx_mt0[lx] + t.m_in_expert;
     t.row0 = tb.lx_base[lx] + t.m_in_expert * kTileM;
     t.rows = max(0, min(kTileM, tb.lx_rows[lx] - t.m_in_expert * kTileM));   // 0: no such M tile
@@ -523,7 +532,7 @@ moe_forward_kernel(const __grid_constant__ MoeParams p, const __grid_constant__ 
             fail(p, FMOE_PHASE_TASK, -3); ok = false; break;
           }
           ticket = static_cast<int>(ctl->pair_ticket[tslot]);
-          mbar_arrive_cluster(map_to_cta(&ctl->pair_empty[tslot], 0));
+          if constexpr (kPair) mbar_arrive_cluster(map_to_cta(&ctl->pair_empty[tslot], 0));
         }
         const Task t = decode(ticket);
         if (leader) {
@@ -531,7 +540,7 @@ moe_forward_kernel(const __grid_constant__ MoeParams p, const __grid_constant__ 
           if (t.kind == kTaskGemm0) {
             const int e = p.local_e[p.rank * nLx + t.lx];
             const uint32_t* arrived = reinterpret_cast<const uint32_t*>(self + p.lay.disp_arrived);
-            const int lo_row = t.m_in_expert * kTileM, hi_row = lo_row + 2 * kTileM;
+            const int lo_row = t.m_in_expert * kTileM, hi_row = lo_row + kGroup * kTileM;
             int off = 0;
             for (int s = 0; s < W && ok; ++s) {
               const int ns = tb.n[s * E + e];
@@ -544,7 +553,7 @@ moe_forward_kernel(const __grid_constant__ MoeParams p, const __grid_constant__ 
             }
           } else if (t.kind == kTaskGemm1) {
             const int mts = tb.lx_mt0[t.lx + 1] - tb.lx_mt0[t.lx];
-            for (int q = 0; q < 2 && ok; ++q) {
+            for (int q = 0; q < kGroup && ok; ++q) {
               if (t.m_in_expert + q >= mts) break;
               if (!wait_counter_gpu(p.gemm0_done + t.mt + q, static_cast<uint32_t>(4 * p.tiles_n0), p)) {
                 fail(p, FMOE_PHASE_GEMM0_DONE, t.mt + q); ok = false;
@@ -552,11 +561,13 @@ moe_forward_kernel(const __grid_constant__ MoeParams p, const __grid_constant__ 
             }
           }
           if (!ok) break;
-          if (!mbar_wait_cluster(&ctl->pair_empty[tslot], ring_par ^ 1, p.abort_word)) {
-            fail(p, FMOE_PHASE_TASK, -4); ok = false; break;
+          if constexpr (kPair) {
+            if (!mbar_wait_cluster(&ctl->pair_empty[tslot], ring_par ^ 1, p.abort_word)) {
+              fail(p, FMOE_PHASE_TASK, -4); ok = false; break;
+            }
+            st_cluster_u32(map_to_cta(&ctl->pair_ticket[tslot], 1), static_cast<uint32_t>(ticket));
+            mbar_arrive_cluster(map_to_cta(&ctl->pair_full[tslot], 1));
           }
-          st_cluster_u32(map_to_cta(&ctl->pair_ticket[tslot], 1), static_cast<uint32_t>(ticket));
-          mbar_arrive_cluster(map_to_cta(&ctl->pair_full[tslot], 1));
         }
         if (!mbar_wait(&ctl->task_empty[tslot], ring_par ^ 1, p.abort_word)) {
           fail(p, FMOE_PHASE_TASK, ticket); ok = false; break;
@@ -569,33 +580,44 @@ moe_forward_kernel(const __grid_constant__ MoeParams p, const __grid_constant__ 
         const bool g0 = t.kind == kTaskGemm0;
         const int nk = g0 ? nk0 : nk1;
         const CUtensorMap* map_a = g0 ? &maps.landing : &maps.y;
-        // this CTA's half of the B tile: GEMM0 gated = gate rows (leader) | up rows (follower)
-        const CUtensorMap* map_b;
-        int brow;
+        // the B tile as two halves of 128 rows: GEMM0 gated = gate rows | up rows.  In a pair the
+        // leader loads the first half and the follower the second; alone, a CTA loads both.
+        const CUtensorMap* map_b0 = g0 ? &maps.up : &maps.down;
+        const CUtensorMap* map_b1 = g0 ? (p.gated ? &maps.up_v : &maps.up) : &maps.down;
+        int brow0, brow1;
         if (g0) {
-          if (p.gated) { map_b = leader ? &maps.up : &maps.up_v; brow = t.lx * p.I + t.n * 128; }
-          else { map_b = &maps.up; brow = t.lx * p.I + t.n * 256 + static_cast<int>(pair_rank) * 128; }
+          if (p.gated) { brow0 = t.lx * p.I + t.n * 128; brow1 = brow0; }
+          else { brow0 = t.lx * p.I + t.n * 256; brow1 = brow0 + 128; }
         } else {
-          map_b = &maps.down; brow = t.lx * p.H + t.n * 256 + static_cast<int>(pair_rank) * 128;
+          brow0 = t.lx * p.H + t.n * 256; brow1 = brow0 + 128;
         }
+        const CUtensorMap* map_b = leader ? map_b0 : map_b1;
+        const int brow = leader ? brow0 : brow1;
         const int b_plane_rows = g0 ? nLx * p.I : nLx * p.H;   // rows of one BF16 plane of the weights
         for (int kb = 0; kb < nk && ok; ++kb) {
           for (int pp = 0; pp < kPairs; ++pp, ++fill) {
             const int pa = kPlanes == 1 ? 0 : kPairA[pp], pb = kPlanes == 1 ? 0 : kPairB[pp];
-            const uint32_t s = fill % kStages;
-            if (!mbar_wait_cluster(&ctl->empty[s], ((fill / kStages) & 1) ^ 1, p.abort_word)) {
+            const uint32_t s = fill % NS;
+            if (!mbar_wait_cluster(&ctl->empty[s], ((fill / NS) & 1) ^ 1, p.abort_word)) {
               fail(p, FMOE_PHASE_PIPE_EMPTY, ticket); ok = false; break;
             }
-            uint8_t* sa = stages + s * kStageBytes;
-            uint8_t* sb = sa + kStageABytes;
+            uint8_t* sa = stages + s * STAGE;
+            uint8_t* sb = sa + SA;
             if (p.debug_flags & 2) {   // timing experiment: no loads, the MMAs chew on stale tiles
               if (leader) mbar_arrive(&ctl->full[s]);
               continue;
             }
-            // the leader's barrier counts the bytes of both CTAs
-            if (leader) mbar_expect_tx(&ctl->full[s], 2 * kStageBytes);
-            tma_load_2d_pair(sa, map_a, &ctl->full[s], kb * kTileK, t.row0 + pa * p.landing_rows);
-            tma_load_2d_pair(sb, map_b, &ctl->full[s], kb * kTileK, brow + pb * b_plane_rows);
+            if constexpr (kPair) {
+              // the leader's barrier counts the bytes of both CTAs
+              if (leader) mbar_expect_tx(&ctl->full[s], 2 * STAGE);
+              tma_load_2d_pair(sa, map_a, &ctl->full[s], kb * kTileK, t.row0 + pa * p.landing_rows);
+              tma_load_2d_pair(sb, map_b, &ctl->full[s], kb * kTileK, brow + pb * b_plane_rows);
+            } else {
+              mbar_expect_tx(&ctl->full[s], STAGE);
+              tma_load_2d(sa, map_a, &ctl->full[s], kb * kTileK, t.row0 + pa * p.landing_rows);
+              tma_load_2d(sb, map_b0, &ctl->full[s], kb * kTileK, brow0 + pb * b_plane_rows);
+              tma_load_2d(sb + SB / 2, map_b1, &ctl->full[s], kb * kTileK, brow1 + pb * b_plane_rows);
+            }
           }
         }
       }
@@ -604,9 +626,9 @@ moe_forward_kernel(const __grid_constant__ MoeParams p, const __grid_constant__ 
         // leader can watch its barriers (bounded), the follower allows the same time to pass
         const long long t_start = clock_now();
         if (leader) {
-          const uint32_t first = fill > kStages ? fill - kStages : 0;
+          const uint32_t first = fill > NS ? fill - NS : 0;
           for (uint32_t f = first; f < fill; ++f)
-            while (!mbar_try_wait_cluster(&ctl->full[f % kStages], (f / kStages) & 1) &&
+            while (!mbar_try_wait_cluster(&ctl->full[f % NS], (f / NS) & 1) &&
                    clock_now() - t_start < 2000000LL) {}
         } else {
           while (clock_now() - t_start < 2000000LL) {}
@@ -615,7 +637,7 @@ moe_forward_kernel(const __grid_constant__ MoeParams p, const __grid_constant__ 
     }
   } else if (ctl->ok && warp == 1) {
     if (lane == 0 && leader) {
-      const uint32_t idesc = umma_idesc_f16(Cvt<T>::kFormat, 2 * kTileM, kUmmaN);
+      const uint32_t idesc = umma_idesc_f16(Cvt<T>::kFormat, kGroup * kTileM, kUmmaN);
       uint32_t fill = 0, tslot = 0, acc_it = 0;
       for (uint32_t it = 0;; ++it, tslot = (tslot + 1) % kTaskSlots) {
         if (!mbar_wait(&ctl->task_full[tslot], (it / kTaskSlots) & 1, p.abort_word)) {
@@ -634,13 +656,13 @@ moe_forward_kernel(const __grid_constant__ MoeParams p, const __grid_constant__ 
         const uint32_t d_corr = ctl->tmem_base + kUmmaN;   // fp32 layers only (single-buffered there)
         bool ok = true;
         for (int kb = 0; kb < nk; ++kb, ++fill) {
-          const uint32_t s = fill % kStages;
-          if (!mbar_wait_cluster(&ctl->full[s], (fill / kStages) & 1, p.abort_word)) {
+          const uint32_t s = fill % NS;
+          if (!mbar_wait_cluster(&ctl->full[s], (fill / NS) & 1, p.abort_word)) {
             fail(p, FMOE_PHASE_PIPE_FULL, t.mt); ok = false; break;
           }
           tc_fence_after_sync();
-          const uint32_t a_addr = smem_u32(stages + s * kStageBytes);
-          const uint32_t b_addr = a_addr + kStageABytes;
+          const uint32_t a_addr = smem_u32(stages + s * STAGE);
+          const uint32_t b_addr = a_addr + SA;
           // fp32 layers: the last pair of every K block is the leading one (planes 0 x 0)
           const bool lead = kPlanes == 1 || (kb % kPairs) == kPairs - 1;
           const uint32_t d = lead ? d_tmem : d_corr;
@@ -648,14 +670,18 @@ moe_forward_kernel(const __grid_constant__ MoeParams p, const __grid_constant__ 
           if (!(p.debug_flags & 1)) {   // flag 1 = timing experiment: loads only, no MMAs
 #pragma unroll
             for (int k = 0; k < kTileK / 16; ++k) {
-              umma_f16_pair(d, umma_desc_sw128(a_addr + k * 32), umma_desc_sw128(b_addr + k * 32),
-                            idesc, (!first || k > 0) ? 1u : 0u);
+              const uint64_t da = umma_desc_sw128(a_addr + k * 32), db = umma_desc_sw128(b_addr + k * 32);
+              if constexpr (kPair) umma_f16_pair(d, da, db, idesc, (!first || k > 0) ? 1u : 0u);
+              else umma_f16(d, da, db, idesc, (!first || k > 0) ? 1u : 0u);
             }
           }
-          umma_commit_pair(&ctl->empty[s], 3);    // frees the stage in both CTAs
+          if constexpr (kPair) umma_commit_pair(&ctl->empty[s], 3);    // frees the stage in both CTAs
+          else umma_commit(&ctl->empty[s]);
         }
         if (!ok) break;
-        umma_commit_pair(&ctl->acc_full[buf], 3); // both CTAs' epilogues may read their rows
+        // this CTA's (both CTAs') epilogue warps may read their rows of the accumulator
+        if constexpr (kPair) umma_commit_pair(&ctl->acc_full[buf], 3);
+        else umma_commit(&ctl->acc_full[buf]);
         ++acc_it;
       }
     }
@@ -663,7 +689,8 @@ moe_forward_kernel(const __grid_constant__ MoeParams p, const __grid_constant__ 
     // epilogue warps: TMEM lane quadrant = warp id mod 4; this CTA's 128 rows of the pair's tile
     const int quad = warp & 3;
     const int row_in_tile = quad * 32 + lane;
-    const uint32_t acc_empty_leader = map_to_cta(&ctl->acc_empty[0], 0);
+    uint32_t acc_empty_leader = 0;
+    if constexpr (kPair) acc_empty_leader = map_to_cta(&ctl->acc_empty[0], 0);
     uint32_t tslot = 0, acc_it = 0;
     for (uint32_t it = 0;; ++it, tslot = (tslot + 1) % kTaskSlots) {
       if (!mbar_wait(&ctl->task_full[tslot], (it / kTaskSlots) & 1, p.abort_word)) {
@@ -686,7 +713,10 @@ moe_forward_kernel(const __grid_constant__ MoeParams p, const __grid_constant__ 
       auto release_acc = [&]() {
         tc_fence_before_sync();
         __syncwarp();
-        if (lane == 0) mbar_arrive_cluster(acc_empty_leader + buf * static_cast<uint32_t>(sizeof(uint64_t)));
+        if (lane == 0) {
+          if constexpr (kPair) mbar_arrive_cluster(acc_empty_leader + buf * static_cast<uint32_t>(sizeof(uint64_t)));
+          else mbar_arrive(&ctl->acc_empty[buf]);
+        }
       };
 
       if (t.kind == kTaskGemm0) {
@@ -863,9 +893,12 @@ moe_forward_kernel(const __grid_constant__ MoeParams p, const __grid_constant__ 
   // ---- leave ------------------------------------------------------------------------------
   tc_fence_before_sync();
   __syncthreads();
-  cluster_sync_all();   // the peer no longer touches this CTA's barriers, tiles or TMEM
+  if constexpr (kPair) cluster_sync_all();   // the peer no longer touches this CTA's barriers, tiles or TMEM
   tc_fence_after_sync();
-  if (warp == 1) tmem_dealloc_pair(ctl->tmem_base, 512);
+  if (warp == 1) {
+    if constexpr (kPair) tmem_dealloc_pair(ctl->tmem_base, 512);
+    else tmem_dealloc(ctl->tmem_base, 512);
+  }
   if (tid == 0) {
     __threadfence();
     const uint32_t prev = atomicAdd(p.done_ctas, 1u);
@@ -877,23 +910,31 @@ moe_forward_kernel(const __grid_constant__ MoeParams p, const __grid_constant__ 
   }
 }
 
+template <typename T>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
+moe_forward_kernel_pair(const __grid_constant__ MoeParams p, const __grid_constant__ TmaMaps maps) {
+  moe_forward_body<T, true>(p, maps);
+}
+template <typename T>
+__global__ void __launch_bounds__(kThreads, 1)
+moe_forward_kernel(const __grid_constant__ MoeParams p, const __grid_constant__ TmaMaps maps) {
+  moe_forward_body<T, false>(p, maps);
+}
+
 }  // namespace
 
 size_t moe_smem_bytes(int W, int E, int nLx) {
-  return 1024 + static_cast<size_t>(kStages) * kStageBytes + sizeof(Control) +
+  return 1024 + static_cast<size_t>(4) * 3 * kStageABytes + sizeof(Control) +
          tables_ints(W, E, nLx) * sizeof(int) + 64;
 }
 
 cudaError_t moe_prepare_kernel(size_t smem) {
-  cudaError_t e = cudaFuncSetAttribute(moe_forward_kernel<__nv_bfloat16>,
-                                       cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       static_cast<int>(smem));
-  if (e != cudaSuccess) return e;
-  e = cudaFuncSetAttribute(moe_forward_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                           static_cast<int>(smem));
-  if (e != cudaSuccess) return e;
-  return cudaFuncSetAttribute(moe_forward_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                              static_cast<int>(smem));
+  const int n = static_cast<int>(smem);
+  cudaError_t e = cudaSuccess;
+  auto set = [&](auto kern) { if (e == cudaSuccess) e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, n); };
+  set(moe_forward_kernel<__nv_bfloat16>); set(moe_forward_kernel<__half>); set(moe_forward_kernel<float>);
+  set(moe_forward_kernel_pair<__nv_bfloat16>); set(moe_forward_kernel_pair<__half>); set(moe_forward_kernel_pair<float>);
+  return e;
 }
 
 namespace {
@@ -921,12 +962,14 @@ cudaError_t launch_moe(const MoeParams& p, const CUtensorMap* maps, int grid, si
                        cudaStream_t stream) {
   TmaMaps m;
   m.landing = maps[0]; m.y = maps[1]; m.up = maps[2]; m.up_v = maps[3]; m.down = maps[4];
-  if (p.elem_bytes == 4) {
-    moe_forward_kernel<float><<<grid, kThreads, smem, stream>>>(p, m);
-  } else if (p.ab_format == 1) {
-    moe_forward_kernel<__nv_bfloat16><<<grid, kThreads, smem, stream>>>(p, m);
+  if (p.pair) {
+    if (p.elem_bytes == 4) moe_forward_kernel_pair<float><<<grid, kThreads, smem, stream>>>(p, m);
+    else if (p.ab_format == 1) moe_forward_kernel_pair<__nv_bfloat16><<<grid, kThreads, smem, stream>>>(p, m);
+    else moe_forward_kernel_pair<__half><<<grid, kThreads, smem, stream>>>(p, m);
   } else {
-    moe_forward_kernel<__half><<<grid, kThreads, smem, stream>>>(p, m);
+    if (p.elem_bytes == 4) moe_forward_kernel<float><<<grid, kThreads, smem, stream>>>(p, m);
+    else if (p.ab_format == 1) moe_forward_kernel<__nv_bfloat16><<<grid, kThreads, smem, stream>>>(p, m);
+    else moe_forward_kernel<__half><<<grid, kThreads, smem, stream>>>(p, m);
   }
   ++g_launches;
   return cudaGetLastError();

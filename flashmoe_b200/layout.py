@@ -28,7 +28,7 @@ class RankLayout:
 
 
 def build(counts: Sequence[Sequence[int]], rank: int, expert_map: Sequence[int], ec: int,
-          tiles_n0: int, tiles_n1: int, grid: int = 148) -> RankLayout:
+          tiles_n0: int, tiles_n1: int, grid: int = 148, pair: bool = True) -> RankLayout:
     """counts[s][e] = tokens of rank s that chose expert e (unclamped, as the router writes them)."""
     W, E = len(counts), len(expert_map)
     nlx = E // W
@@ -52,14 +52,15 @@ def build(counts: Sequence[Sequence[int]], rank: int, expert_map: Sequence[int],
     lag = 1
     while lag < nlx and mtile0[lag] * tiles_n0 < 2 * grid:
         lag += 1
+    gsz = 2 if pair else 1     # M tiles per ticket: a CTA pair takes two, a lone CTA one
     tasks = []
     for i in range(nlx + lag):
         if i < nlx:
-            groups = (mtile0[i + 1] - mtile0[i] + 1) // 2
+            groups = (mtile0[i + 1] - mtile0[i] + gsz - 1) // gsz
             tasks += [(0, i, g, n) for n in range(tiles_n0) for g in range(groups)]
         if i >= lag:
             j = i - lag
-            groups = (mtile0[j + 1] - mtile0[j] + 1) // 2
+            groups = (mtile0[j + 1] - mtile0[j] + gsz - 1) // gsz
             tasks += [(1, j, g, n) for n in range(tiles_n1) for g in range(groups)]
     return RankLayout(sent, dst_row0, lx_base, lx_rows, mtile0, tasks)
 

@@ -196,6 +196,8 @@ typedef struct fmoe_geometry {
   int32_t landing_rows;    /* rows of the token landing area */
   int32_t grid, threads;   /* launch shape of the persistent kernel */
   int32_t smem_bytes;
+  int32_t cta_pairs;       /* 1: tiles are worked by CTA pairs (cta_group::2), 0: by single CTAs */
+  int32_t reserved;
   int64_t symm_bytes, workspace_bytes;
 } fmoe_geometry;
 int fmoe_get_geometry(const fmoe_ctx* ctx, fmoe_geometry* out);

@@ -135,3 +135,5 @@ def test_layout_matches_hand_computed_example():
     # a wider grid makes GEMM1 trail by more experts: all GEMM0 tiles first here
     wide = layout.build(counts, 1, [0, 0, 1, 1], ec=128, tiles_n0=2, tiles_n1=1, grid=148)
     assert [(t[0], t[1]) for t in wide.tasks] == kinds
+    lone = layout.build(counts, 1, [0, 0, 1, 1], ec=128, tiles_n0=2, tiles_n1=1, grid=1, pair=False)
+    assert [(t[0], t[1]) for t in lone.tasks] == [(0, 0)] * 2 + [(0, 1)] * 4 + [(1, 0)] * 1 + [(1, 1)] * 2
