@@ -281,6 +281,7 @@ def main() -> int:
     barrier()
     launches = lib.fmoe_launch_count() - launches0
     layer.check()
+    phases = layer.phases()   # in-kernel %globaltimer stamps of the last timed launch
     ms_step = max_over_ranks(ev0.elapsed_time(ev1) / a.steps)
     ms_kernel = max_over_ranks(statistics.mean(s.elapsed_time(e) for s, e in kev))
 
@@ -360,7 +361,7 @@ def main() -> int:
             "e2e": {"value": tokens_job / e2e_s, "unit": "tokens/s", "ms_per_step": e2e_s * 1e3,
                     "h2d_bytes_per_step": S * H * eb, "d2h_bytes_per_step": S * H * eb,
                     "api": "fmoe_forward_host (C ABI, pinned host buffers)"},
-            "gpu_launches": int(launches), "roofline": roofline, "cpu_baseline": cpu, "clocks": clocks}
+            "gpu_launches": int(launches), "phases_us": phases, "roofline": roofline, "cpu_baseline": cpu, "clocks": clocks}
     print(json.dumps(line))
     return 0
 

@@ -268,6 +268,7 @@ int fmoe_ctx_create(const fmoe_model_desc* model, const fmoe_ep_desc* ep, void* 
   const size_t w_done = w; w = align_up(w + sizeof(uint32_t) * max_mtiles, 256);
   const size_t w_ctl = w; w = align_up(w + 256, 256);   // ticket, done_ctas, abort, epoch
   const size_t w_status = w; w = align_up(w + sizeof(fmoe_status), 256);
+  const size_t w_trace = w; w = align_up(w + sizeof(unsigned long long) * 8 * 256, 256);
   const size_t w_table = w; w = align_up(w + sizeof(TokenSlot) * E * g.round_ec, 256);
   const size_t w_routes = w; w = align_up(w + sizeof(Route) * S * k, 256);
   const size_t w_owner = w; w = align_up(w + sizeof(int32_t) * E, 256);
@@ -291,11 +292,13 @@ int fmoe_ctx_create(const fmoe_model_desc* model, const fmoe_ep_desc* ep, void* 
   p.gated = gated ? 1 : 0; p.act = model->act_type; p.ab_format = model->data_type == FMOE_DT_FP16 ? 0 : 1;
   p.elem_bytes = c->eb;
   { const char* dbg = std::getenv("FMOE_DEBUG"); p.debug_flags = dbg ? std::atoi(dbg) : 0; }
-  // CTA pairs pay off when experts hold several M tiles; with <= ~1 tile per expert a lone CTA per
-  // tile keeps more weight bytes in flight.  Expected rows per expert if routing is balanced:
+  // Two forms of the GEMM loop exist: every CTA alone on a 128 x 256 tile (default), or CTA pairs
+  // on 256 x 256 tiles with tcgen05.mma.cta_group::2 (FMOE_PAIR=1).  Measured on one B200 the pair
+  // form gains 3-6 % per unit of MMA work on experts with many M tiles and loses more than that
+  // to its coarser 256-row granularity and to the fewer weight bytes it keeps in flight when
+  // experts hold about one tile, so it is opt-in.
   {
-    const double rows_per_expert = static_cast<double>(W) * S * k / E;
-    p.pair = rows_per_expert >= 192.0 ? 1 : 0;
+    p.pair = 0;
     const char* force = std::getenv("FMOE_PAIR");
     if (force) p.pair = std::atoi(force) ? 1 : 0;
     g.cta_pairs = p.pair; g.stages = p.pair ? 6 : 4;
@@ -314,6 +317,7 @@ int fmoe_ctx_create(const fmoe_model_desc* model, const fmoe_ep_desc* ep, void* 
   p.abort_word = reinterpret_cast<uint32_t*>(c->work + w_ctl + 128);
   p.epoch = reinterpret_cast<uint64_t*>(c->work + w_ctl + 192);
   p.status = reinterpret_cast<fmoe_status*>(c->work + w_status);
+  p.trace = reinterpret_cast<unsigned long long*>(c->work + w_trace);
   p.table = reinterpret_cast<const TokenSlot*>(c->work + w_table);
   p.routes = reinterpret_cast<const Route*>(c->work + w_routes);
 
@@ -415,6 +419,7 @@ int fmoe_debug_buffer(fmoe_ctx* ctx, int32_t which, void** ptr_out, size_t* byte
     case 2: *ptr_out = p.y; *bytes_out = static_cast<size_t>(ctx->planes) * p.landing_rows * p.I * 2; break;
     case 3: *ptr_out = ctx->symm + ctx->lay.ret; *bytes_out = static_cast<size_t>(p.S) * p.k * p.H * ctx->eb; break;
     case 4: *ptr_out = const_cast<Route*>(p.routes); *bytes_out = sizeof(Route) * p.S * p.k; break;
+    case 5: *ptr_out = p.trace; *bytes_out = sizeof(unsigned long long) * 8 * ctx->geo.grid; break;
     default: return set_error(FMOE_ERR_INVALID_ARG, "unknown buffer id");
   }
   return FMOE_OK;

@@ -76,6 +76,7 @@ struct MoeParams {
   uint64_t* epoch;         // forward number, bumped by the last CTA to leave
   uint32_t* abort_word;
   fmoe_status* status;
+  unsigned long long* trace;  // [grid][8] %globaltimer stamps of the last forward, per CTA
 
   const TokenSlot* table;  // [E][round_ec]
   const Route* routes;     // [S][k]

@@ -308,6 +308,16 @@ __device__ __forceinline__ void moe_forward_body(const MoeParams& p, const TmaMa
   __syncthreads();
   if constexpr (kPair) cluster_sync_all();   // the peer's barriers exist before anything arrives on them
   tc_fence_after_sync();
+  // per-CTA phase stamps (%globaltimer, ns): 0 start, 1 counts of all ranks in, 2 tables built,
+  // 3 dispatch done, 4 first ticket drawn, 5 last ticket (stop) seen, 6 returns all in, 7 combine done
+  auto stamp = [&](int i) {
+    if (tid == 0) {
+      unsigned long long t;
+      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+      p.trace[static_cast<size_t>(blockIdx.x) * 8 + i] = t;
+    }
+  };
+  stamp(0);
   const uint64_t epoch = ctl->epoch;
   const uint64_t flag_val = epoch + 1;
   const int parity = static_cast<int>(epoch & 1);
@@ -347,6 +357,7 @@ __device__ __forceinline__ void moe_forward_body(const MoeParams& p, const TmaMa
     if (!ok) { fail(p, FMOE_PHASE_COUNTS, tid); ctl->ok = 0; }
   }
   __syncthreads();
+  stamp(1);
   if (ctl->ok) {
     const int32_t* t = reinterpret_cast<const int32_t*>(self + p.lay.cnt_table) +
                        static_cast<size_t>(parity) * W * E;
@@ -415,6 +426,7 @@ __device__ __forceinline__ void moe_forward_body(const MoeParams& p, const TmaMa
     ctl->total_tasks = first;
   }
   __syncthreads();
+  stamp(2);
 
   // ---- dispatch: push this rank's routed rows to the experts' owners --------------------
   if (ctl->ok) {
@@ -480,6 +492,7 @@ __device__ __forceinline__ void moe_forward_body(const MoeParams& p, const TmaMa
     }
   }
 
+  stamp(3);
   // ---- expert GEMMs ---------------------------------------------------------------------
   // Two CTAs (a cluster of 2, on the two SMs of one TPC) work on one 256 x 256 output tile:
   // each loads its own 128 rows of A and its own half of the B tile, the leader issues
@@ -522,6 +535,7 @@ __device__ __forceinline__ void moe_forward_body(const MoeParams& p, const TmaMa
       uint32_t fill = 0;  // stage fills issued so far
       uint32_t tslot = 0;
       bool ok = true;
+      stamp(4);
       for (uint32_t it = 0; ok; ++it, tslot = (tslot + 1) % kTaskSlots) {
         const uint32_t ring_par = (it / kTaskSlots) & 1;
         int ticket;
@@ -574,7 +588,7 @@ __device__ __forceinline__ void moe_forward_body(const MoeParams& p, const TmaMa
         }
         ctl->tasks[tslot] = t;
         mbar_arrive(&ctl->task_full[tslot]);
-        if (t.kind == kTaskStop) break;
+        if (t.kind == kTaskStop) { stamp(5); break; }
         fence_proxy_async();
 
         const bool g0 = t.kind == kTaskGemm0;
@@ -842,6 +856,7 @@ __device__ __forceinline__ void moe_forward_body(const MoeParams& p, const TmaMa
     }
   }
   __syncthreads();
+  stamp(6);
   if (ctl->ok && *reinterpret_cast<volatile uint32_t*>(p.abort_word) == 0) {
     const int G = gridDim.x * (kThreads / 32);
     const int vecs = p.H * EB / 16;
@@ -891,6 +906,7 @@ __device__ __forceinline__ void moe_forward_body(const MoeParams& p, const TmaMa
   }
 
   // ---- leave ------------------------------------------------------------------------------
+  stamp(7);
   tc_fence_before_sync();
   __syncthreads();
   if constexpr (kPair) cluster_sync_all();   // the peer no longer touches this CTA's barriers, tiles or TMEM

@@ -56,6 +56,24 @@ def test_fp32_reference_configuration():
         layer.close()
 
 
+@pytest.mark.parametrize("name", ["bf16_two_mtiles", "bf16_gated_k2", "fp32_gated_k2"])
+def test_cta_pair_form_of_the_gemm_loop(name, monkeypatch):
+    """FMOE_PAIR=1 selects the tcgen05.mma.cta_group::2 form (CTA pairs on 256-row tile groups);
+    it must give the same answers as the default form."""
+    monkeypatch.setenv("FMOE_PAIR", "1")
+    w = GOLDEN_CASES[name]
+    lw, x = make_weights(w), make_tokens(w)
+    ref, _ = oracle_layer(w, x=x, lw=lw)
+    layer = make_layer(w, lw)
+    try:
+        assert layer.geometry().cta_pairs == 1
+        for _ in range(2):
+            out = layer.forward(x).cpu()
+            assert max_rel_err(out, ref) <= REL_TOL[int(w.data_type)]
+    finally:
+        layer.close()
+
+
 def test_stages_dispatch_gemm0_gemm1():
     """Checks the intermediate buffers: landed rows (exact), GEMM0 output and returned rows."""
     w = GOLDEN_CASES["bf16_gated_k2"]
