@@ -79,7 +79,7 @@ struct Control {
   Task tasks[kTaskSlots];
   uint32_t tmem_base;
   uint32_t ok;            // cleared when a CTA-wide wait failed
-  int total_tasks, n_segs, send_rows, expected_ret;
+  int total_tasks, n_segs, send_rows, expected_ret, lag;
   uint64_t epoch;
 };
 
@@ -380,50 +380,81 @@ __device__ __forceinline__ void moe_forward_body(const MoeParams& p, const TmaMa
     }
   }
   __syncthreads();
-  if (ctl->ok && tid < W) {
-    // landing-row base of every expert at its owner: that owner's experts in local order,
-    // each rounded up to whole M tiles
-    const int r = tid;
-    int base = 0;
-    for (int lx = 0; lx < nLx; ++lx) {
-      const int e = p.local_e[r * nLx + lx];
-      const int tot = tb.tot[e];
-      tb.dst_row0[e] += base;
-      if (r == p.rank) { tb.lx_base[lx] = base; tb.lx_rows[lx] = tot; }
-      base += (tot + kTileM - 1) / kTileM * kTileM;
+  // exclusive prefix sums by one warp, 32 entries per step: emit(i, sum of values before i)
+  auto warp_scan = [&](auto value_of, auto emit, int n) -> int {   // returns the total
+    int carry = 0;
+    for (int base = 0; base < n; base += 32) {
+      const int i = base + lane;
+      const int v = i < n ? value_of(i) : 0;
+      int incl = v;
+#pragma unroll
+      for (int off = 1; off < 32; off <<= 1) {
+        const int u = __shfl_up_sync(0xffffffffu, incl, off);
+        if (lane >= off) incl += u;
+      }
+      if (i < n) emit(i, carry + incl - v);
+      carry += __shfl_sync(0xffffffffu, incl, 31);
+    }
+    return carry;
+  };
+  if (ctl->ok) {
+    // landing-row base of every expert at its owner: that owner's experts in local order, each
+    // rounded up to whole M tiles (one warp per owner rank)
+    for (int r = warp; r < W; r += kThreads / 32) {
+      warp_scan([&](int lx) { return (tb.tot[p.local_e[r * nLx + lx]] + kTileM - 1) / kTileM * kTileM; },
+                [&](int lx, int base) {
+                  const int e = p.local_e[r * nLx + lx];
+                  tb.dst_row0[e] += base;
+                  if (r == p.rank) { tb.lx_base[lx] = base; tb.lx_rows[lx] = tb.tot[e]; }
+                }, nLx);
     }
   }
   __syncthreads();
-  if (ctl->ok && tid == 0) {
-    int sp = 0;
-    for (int e = 0; e < E; ++e) { tb.send_pref[e] = sp; sp += tb.n[p.rank * E + e]; }
-    tb.send_pref[E] = sp;
-    ctl->send_rows = sp;
-    ctl->expected_ret = sp * p.tiles_n1;
-    int mt = 0;
-    for (int lx = 0; lx < nLx; ++lx) { tb.lx_mt0[lx] = mt; mt += (tb.lx_rows[lx] + kTileM - 1) / kTileM; }
-    tb.lx_mt0[nLx] = mt;
-    // task order: GEMM1 of expert i trails GEMM0 of expert i by `lag` experts, the smallest lag
-    // whose GEMM0 tiles cover two tickets per CTA, so that by the time a GEMM1 ticket is drawn the
-    // GEMM0 tiles it depends on are long finished: G0(0..lag-1), G0(lag), G1(0), G0(lag+1), G1(1), ...
-    // A ticket is a group of kGroup M tiles (one per CTA of a pair) times one N tile.
-    int lag = 1;
-    while (lag < nLx && tb.lx_mt0[lag] * p.tiles_n0 < 2 * static_cast<int>(gridDim.x)) ++lag;
-    int ns = 0, first = 0;
-    for (int i = 0; i < nLx + lag; ++i) {
-      if (i < nLx) {
-        tb.seg_first[ns] = first; tb.seg_kind[ns] = kTaskGemm0; tb.seg_lx[ns] = i; ++ns;
-        first += (tb.lx_mt0[i + 1] - tb.lx_mt0[i] + kGroup - 1) / kGroup * p.tiles_n0;
-      }
-      if (i >= lag) {
-        const int j = i - lag;
-        tb.seg_first[ns] = first; tb.seg_kind[ns] = kTaskGemm1; tb.seg_lx[ns] = j; ++ns;
-        first += (tb.lx_mt0[j + 1] - tb.lx_mt0[j] + kGroup - 1) / kGroup * p.tiles_n1;
-      }
+  if (ctl->ok && warp == 0) {
+    const int sp = warp_scan([&](int e) { return tb.n[p.rank * E + e]; },
+                             [&](int e, int v) { tb.send_pref[e] = v; }, E);
+    const int mt = warp_scan([&](int lx) { return (tb.lx_rows[lx] + kTileM - 1) / kTileM; },
+                             [&](int lx, int v) { tb.lx_mt0[lx] = v; }, nLx);
+    if (lane == 0) {
+      tb.send_pref[E] = sp;
+      tb.lx_mt0[nLx] = mt;
+      ctl->send_rows = sp;
+      ctl->expected_ret = sp * p.tiles_n1;
+      ctl->lag = nLx;
     }
-    tb.seg_first[ns] = first;
-    ctl->n_segs = ns;
-    ctl->total_tasks = first;
+  }
+  __syncthreads();
+  // task order: GEMM1 of expert i trails GEMM0 of expert i by `lag` experts, the smallest lag
+  // whose GEMM0 tiles cover two tickets per CTA, so that by the time a GEMM1 ticket is drawn the
+  // GEMM0 tiles it depends on are long finished: G0(0..lag-1), G0(lag), G1(0), G0(lag+1), G1(1), ...
+  if (ctl->ok) {
+    for (int t = 1 + tid; t < nLx; t += kThreads)
+      if (tb.lx_mt0[t] * p.tiles_n0 >= 2 * static_cast<int>(gridDim.x)) atomicMin(&ctl->lag, t);
+  }
+  __syncthreads();
+  if (ctl->ok) {
+    // A ticket is a group of kGroup M tiles (one per CTA of a pair) times one N tile.  Step s of the
+    // order emits G0(s) (s < nLx) and then G1(s - lag) (s >= lag); sizes go to seg_first and are
+    // turned into first-ticket numbers by the scan below.
+    const int lag = ctl->lag;
+    for (int i = tid; i < nLx; i += kThreads) {
+      const int groups = (tb.lx_mt0[i + 1] - tb.lx_mt0[i] + kGroup - 1) / kGroup;
+      const int i0 = i + max(0, i - lag);                                   // G0(i)
+      const int s1 = i + lag;
+      const int i1 = min(s1, nLx) + i + (s1 < nLx ? 1 : 0);                 // G1(i)
+      tb.seg_first[i0] = groups * p.tiles_n0; tb.seg_kind[i0] = kTaskGemm0; tb.seg_lx[i0] = i;
+      tb.seg_first[i1] = groups * p.tiles_n1; tb.seg_kind[i1] = kTaskGemm1; tb.seg_lx[i1] = i;
+    }
+  }
+  __syncthreads();
+  if (ctl->ok && warp == 0) {
+    const int total = warp_scan([&](int i) { return tb.seg_first[i]; },
+                                [&](int i, int v) { tb.seg_first[i] = v; }, 2 * nLx);
+    if (lane == 0) {
+      tb.seg_first[2 * nLx] = total;
+      ctl->n_segs = 2 * nLx;
+      ctl->total_tasks = total;
+    }
   }
   __syncthreads();
   stamp(2);
@@ -448,43 +479,56 @@ __device__ __forceinline__ void moe_forward_body(const MoeParams& p, const TmaMa
       const int r = p.owner[e], lx = p.lidx[e];
       char* peer = p.peers[r];
       const int run_start = q;
-      for (; q < run_end; ++q) {
-        const int j = q - tb.send_pref[e];
-        const uint32_t token = p.table[static_cast<size_t>(e) * p.round_ec + j].token;
-        const int drow = tb.dst_row0[e] + j;
-        const uint4* src = tok_base + static_cast<size_t>(token) * vecs;
-        if constexpr (kPlanes == 1) {
-          uint4* dst = reinterpret_cast<uint4*>(peer + p.lay.landing) + static_cast<size_t>(drow) * vecs;
-          for (int v = lane; v < vecs; v += 32) dst[v] = __ldg(src + v);
-        } else {
-          // fp32 row -> three BF16 planes at the owner (4 floats in, 3 x 8 bytes out)
-          for (int v = lane; v < vecs; v += 32) {
-            const uint4 raw = __ldg(src + v);
-            const float f[4] = {__uint_as_float(raw.x), __uint_as_float(raw.y), __uint_as_float(raw.z),
-                                __uint_as_float(raw.w)};
-            unsigned short q[4][3];
+      while (q < run_end) {
+        // up to 32 rows at a time: lane i fetches row (q + i)'s token id and which of the token's
+        // k choices this expert is, so that the copies below do not wait on those look-ups
+        const int batch = min(32, run_end - q);
+        uint32_t my_token = 0, my_choice = 0;
+        if (lane < batch) {
+          my_token = p.table[static_cast<size_t>(e) * p.round_ec + (q - tb.send_pref[e]) + lane].token;
+          for (int c = 0; c < p.k; ++c)
+            if (p.routes[static_cast<size_t>(my_token) * p.k + c].expert == e) { my_choice = c; break; }
+        }
+        for (int i = 0; i < batch; ++i) {
+          const uint32_t token = __shfl_sync(0xffffffffu, my_token, i);
+          const uint32_t choice = __shfl_sync(0xffffffffu, my_choice, i);
+          const int drow = tb.dst_row0[e] + (q - tb.send_pref[e]) + i;
+          const uint4* src = tok_base + static_cast<size_t>(token) * vecs;
+          if constexpr (kPlanes == 1) {
+            uint4* dst = reinterpret_cast<uint4*>(peer + p.lay.landing) + static_cast<size_t>(drow) * vecs;
+            for (int v0 = lane; v0 < vecs; v0 += 128) {   // four loads in flight per lane
+              uint4 x[4];
 #pragma unroll
-            for (int i = 0; i < 4; ++i) split3(f[i], q[i]);
+              for (int u = 0; u < 4; ++u) if (v0 + 32 * u < vecs) x[u] = __ldg(src + v0 + 32 * u);
 #pragma unroll
-            for (int pl = 0; pl < 3; ++pl) {
-              uint2* dst = reinterpret_cast<uint2*>(peer + p.lay.landing + pl * landing_plane) +
-                           static_cast<size_t>(drow) * vecs + v;
-              *dst = make_uint2(static_cast<uint32_t>(q[0][pl]) | (static_cast<uint32_t>(q[1][pl]) << 16),
-                                static_cast<uint32_t>(q[2][pl]) | (static_cast<uint32_t>(q[3][pl]) << 16));
+              for (int u = 0; u < 4; ++u) if (v0 + 32 * u < vecs) dst[v0 + 32 * u] = x[u];
+            }
+          } else {
+            // fp32 row -> three BF16 planes at the owner (4 floats in, 3 x 8 bytes out)
+            for (int v = lane; v < vecs; v += 32) {
+              const uint4 raw = __ldg(src + v);
+              const float f[4] = {__uint_as_float(raw.x), __uint_as_float(raw.y), __uint_as_float(raw.z),
+                                  __uint_as_float(raw.w)};
+              unsigned short h[4][3];
+#pragma unroll
+              for (int z = 0; z < 4; ++z) split3(f[z], h[z]);
+#pragma unroll
+              for (int pl = 0; pl < 3; ++pl) {
+                uint2* dst = reinterpret_cast<uint2*>(peer + p.lay.landing + pl * landing_plane) +
+                             static_cast<size_t>(drow) * vecs + v;
+                *dst = make_uint2(static_cast<uint32_t>(h[0][pl]) | (static_cast<uint32_t>(h[1][pl]) << 16),
+                                  static_cast<uint32_t>(h[2][pl]) | (static_cast<uint32_t>(h[3][pl]) << 16));
+              }
             }
           }
+          if (lane == 0)
+            reinterpret_cast<uint32_t*>(peer + p.lay.landing_meta)[drow] =
+                (static_cast<uint32_t>(p.rank) << kMetaSrcShift) | (token * p.k + choice);
         }
-        int choice = 0;
-        if (lane < p.k) choice = (p.routes[static_cast<size_t>(token) * p.k + lane].expert == e) ? 1 : 0;
-        const unsigned b = __ballot_sync(0xffffffffu, choice != 0);
-        if (lane == 0) {
-          const uint32_t c = b ? static_cast<uint32_t>(__ffs(b) - 1) : 0u;
-          reinterpret_cast<uint32_t*>(peer + p.lay.landing_meta)[drow] =
-              (static_cast<uint32_t>(p.rank) << kMetaSrcShift) | (token * p.k + c);
-        }
+        q += batch;
       }
       const int sent = run_end - run_start;
-      __threadfence_system();
+      // every lane's stores happen before the barrier, the barrier before lane 0's release
       __syncwarp();
       if (lane == 0 && sent > 0)
         red_add_release_sys(reinterpret_cast<uint32_t*>(peer + p.lay.disp_arrived) + p.rank * nLx + lx,
@@ -862,43 +906,65 @@ __device__ __forceinline__ void moe_forward_body(const MoeParams& p, const TmaMa
     const int vecs = p.H * EB / 16;
     const uint4* ret = reinterpret_cast<const uint4*>(self + p.lay.ret);
     uint4* out = static_cast<uint4*>(p.out);
+    constexpr int kPer = 16 / EB;   // elements per 16-byte vector
     for (int tkn = blockIdx.x * (kThreads / 32) + warp; tkn < p.S; tkn += G) {
+      // lane j holds the token's j-th route; a dropped pair gets weight-slot -1
+      Route mine{0, p.EC, 0.0f, 0};
+      if (lane < p.k) mine = p.routes[static_cast<size_t>(tkn) * p.k + lane];
+      const unsigned live = __ballot_sync(0xffffffffu, lane < p.k && mine.slot < p.EC);
       if (p.k == 1) {
-        const Route r = p.routes[tkn];
-        if (r.slot < p.EC) {
-          for (int v = lane; v < vecs; v += 32)
-            out[static_cast<size_t>(tkn) * vecs + v] = __ldcg(ret + static_cast<size_t>(tkn) * vecs + v);
+        if (live & 1u) {
+          const uint4* src = ret + static_cast<size_t>(tkn) * vecs;
+          uint4* dst = out + static_cast<size_t>(tkn) * vecs;
+          for (int v0 = lane; v0 < vecs; v0 += 128) {   // four loads in flight per lane
+            uint4 x[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) if (v0 + 32 * u < vecs) x[u] = __ldcg(src + v0 + 32 * u);
+#pragma unroll
+            for (int u = 0; u < 4; ++u) if (v0 + 32 * u < vecs) dst[v0 + 32 * u] = x[u];
+          }
         }
       } else {
-        for (int v = lane; v < vecs; v += 32) {
-          constexpr int kPer = 16 / EB;   // elements per 16-byte vector
-          float acc[kPer];
+        for (int v0 = lane; v0 < vecs; v0 += 64) {      // two vectors x k rows in flight per lane
+          float acc[2][kPer];
 #pragma unroll
-          for (int i = 0; i < kPer; ++i) acc[i] = 0.0f;
+          for (int u = 0; u < 2; ++u)
+#pragma unroll
+            for (int i = 0; i < kPer; ++i) acc[u][i] = 0.0f;
           for (int j = 0; j < p.k; ++j) {
-            const Route r = p.routes[static_cast<size_t>(tkn) * p.k + j];
-            if (r.slot >= p.EC) continue;
-            const uint4 x = __ldcg(ret + (static_cast<size_t>(tkn) * p.k + j) * vecs + v);
-            const uint32_t w4[4] = {x.x, x.y, x.z, x.w};
-            if constexpr (EB == 2) {
+            const float wj = __shfl_sync(0xffffffffu, mine.weight, j);
+            if (!((live >> j) & 1u)) continue;
+            const uint4* src = ret + (static_cast<size_t>(tkn) * p.k + j) * vecs;
+            uint4 x[2];
 #pragma unroll
-              for (int i = 0; i < 4; ++i) {
-                acc[2 * i] = __fadd_rn(acc[2 * i], __fmul_rn(Cvt<T>::up(w4[i] & 0xffffu), r.weight));
-                acc[2 * i + 1] = __fadd_rn(acc[2 * i + 1], __fmul_rn(Cvt<T>::up(w4[i] >> 16), r.weight));
+            for (int u = 0; u < 2; ++u) if (v0 + 32 * u < vecs) x[u] = __ldcg(src + v0 + 32 * u);
+#pragma unroll
+            for (int u = 0; u < 2; ++u) {
+              const uint32_t w4[4] = {x[u].x, x[u].y, x[u].z, x[u].w};
+              if constexpr (EB == 2) {
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                  acc[u][2 * i] = __fadd_rn(acc[u][2 * i], __fmul_rn(Cvt<T>::up(w4[i] & 0xffffu), wj));
+                  acc[u][2 * i + 1] = __fadd_rn(acc[u][2 * i + 1], __fmul_rn(Cvt<T>::up(w4[i] >> 16), wj));
+                }
+              } else {
+#pragma unroll
+                for (int i = 0; i < 4; ++i) acc[u][i] = __fadd_rn(acc[u][i], __fmul_rn(__uint_as_float(w4[i]), wj));
               }
-            } else {
-#pragma unroll
-              for (int i = 0; i < 4; ++i) acc[i] = __fadd_rn(acc[i], __fmul_rn(__uint_as_float(w4[i]), r.weight));
             }
           }
-          if constexpr (EB == 2) {
-            out[static_cast<size_t>(tkn) * vecs + v] =
-                make_uint4(Cvt<T>::pack(acc[0], acc[1]), Cvt<T>::pack(acc[2], acc[3]),
-                           Cvt<T>::pack(acc[4], acc[5]), Cvt<T>::pack(acc[6], acc[7]));
-          } else {
-            out[static_cast<size_t>(tkn) * vecs + v] =
-                make_uint4(__float_as_uint(acc[0]), __float_as_uint(acc[1]), __float_as_uint(acc[2]),
-                           __float_as_uint(acc[3]));
+#pragma unroll
+          for (int u = 0; u < 2; ++u) {
+            if (v0 + 32 * u >= vecs) continue;
+            uint4 o;
+            if constexpr (EB == 2) {
+              o = make_uint4(Cvt<T>::pack(acc[u][0], acc[u][1]), Cvt<T>::pack(acc[u][2], acc[u][3]),
+                             Cvt<T>::pack(acc[u][4], acc[u][5]), Cvt<T>::pack(acc[u][6], acc[u][7]));
+            } else {
+              o = make_uint4(__float_as_uint(acc[u][0]), __float_as_uint(acc[u][1]), __float_as_uint(acc[u][2]),
+                             __float_as_uint(acc[u][3]));
+            }
+            out[static_cast<size_t>(tkn) * vecs + v0 + 32 * u] = o;
           }
         }
       }
