@@ -141,21 +141,30 @@ __device__ __forceinline__ void vec8_from_smem<float>(const float* p, float (&f)
 // in chunks of 256 elements (one 8-element vector per lane).  The EG x 256 chunk of the router
 // weight is staged in shared memory (cp.async, double buffered) and shared by all warps, so the
 // weight matrix crosses L2 once per CTA instead of once per warp.
-template <typename T, int TT, int EG, int WARPS>
-__global__ void __launch_bounds__(WARPS * 32)
+//
+// The CTA's warps form TG token groups x ES expert parts: warp (tg, part) accumulates, for its TT
+// tokens, the EG / ES experts of every group that fall in its part.  Splitting the experts over
+// warps keeps the accumulators small (TT * EG / ES registers) and puts 4 * ES warps on the SM,
+// which is what hides the FMA and shared-memory latencies when E is large.
+template <typename T, int TT, int EG, int TG, int ES>
+__global__ void __launch_bounds__(TG * ES * 32)
 router_topk_kernel(const RouterParams p) {
+  constexpr int WARPS = TG * ES;
+  constexpr int EP = EG / ES;                        // experts of a group one warp accumulates
+  static_assert(EG % ES == 0, "expert group must split evenly");
   extern __shared__ __align__(16) unsigned char s_raw[];
-  float* s_row = reinterpret_cast<float*>(s_raw);  // [WARPS][TT][E]: logits, then exp, then probabilities
+  float* s_row = reinterpret_cast<float*>(s_raw);  // [TG][TT][E]: logits, then exp, then probabilities
   const int H = p.H, E = p.E;
-  T* wbuf = reinterpret_cast<T*>(s_raw + ((static_cast<size_t>(WARPS) * TT * E * sizeof(float) + 15) & ~size_t(15)));
+  T* wbuf = reinterpret_cast<T*>(s_raw + ((static_cast<size_t>(TG) * TT * E * sizeof(float) + 15) & ~size_t(15)));
   constexpr int kChunk = 256;                       // elements of H per step
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int t0 = (blockIdx.x * WARPS + warp) * TT;
+  const int tg = warp % TG, part = warp / TG;
+  const int t0 = (blockIdx.x * TG + tg) * TT;
   const int nvec = H >> 3;
   const int iters = (nvec + 31) >> 5;
   const T* __restrict__ X = static_cast<const T*>(p.tokens);
   const T* __restrict__ Wr = static_cast<const T*>(p.weights);
-  float* rows = s_row + static_cast<size_t>(warp) * TT * E;
+  float* rows = s_row + static_cast<size_t>(tg) * TT * E;
 
   auto stage = [&](int eg, int it, int buf) {
     const int v = it * 32 + lane;
@@ -174,11 +183,11 @@ router_topk_kernel(const RouterParams p) {
   };
 
   for (int eg = 0; eg < E; eg += EG) {
-    float acc[TT][EG];
+    float acc[TT][EP];
 #pragma unroll
     for (int t = 0; t < TT; ++t)
 #pragma unroll
-      for (int e = 0; e < EG; ++e) acc[t][e] = 0.0f;
+      for (int e = 0; e < EP; ++e) acc[t][e] = 0.0f;
 
     stage(eg, 0, 0);
     for (int it = 0; it < iters; ++it) {
@@ -192,9 +201,9 @@ router_topk_kernel(const RouterParams p) {
           const int tok = min(t0 + t, p.S - 1);  // ragged last group: recompute the last token
           Vec8<T>::load(X + static_cast<size_t>(tok) * H + v * 8, xv[t]);
         }
-        const T* wb = wbuf + static_cast<size_t>(it & 1) * EG * kChunk + lane * 8;
+        const T* wb = wbuf + (static_cast<size_t>(it & 1) * EG + part * EP) * kChunk + lane * 8;
 #pragma unroll
-        for (int e = 0; e < EG; ++e) {
+        for (int e = 0; e < EP; ++e) {
           float wv[8];
           vec8_from_smem<T>(wb + e * kChunk, wv);
 #pragma unroll
@@ -215,19 +224,20 @@ router_topk_kernel(const RouterParams p) {
 #pragma unroll
     for (int t = 0; t < TT; ++t) {
 #pragma unroll
-      for (int e = 0; e < EG; ++e) {
+      for (int e = 0; e < EP; ++e) {
+        const int ex = eg + part * EP + e;
         const float s = butterfly_sum(acc[t][e]);
-        if (lane == ((eg + e) & 31)) {
-          const float b = p.logit_bias ? __ldg(p.logit_bias + eg + e) : 0.0f;
-          rows[t * E + eg + e] = p.logit_bias ? __fadd_rn(s, b) : s;
+        if (lane == (ex & 31)) {
+          const float b = p.logit_bias ? __ldg(p.logit_bias + ex) : 0.0f;
+          rows[t * E + ex] = p.logit_bias ? __fadd_rn(s, b) : s;
         }
       }
     }
   }
-  __syncwarp();
+  __syncthreads();   // a token's logits come from all ES parts
   if (t0 >= p.S) return;
 
-  for (int t = 0; t < TT; ++t) {
+  for (int t = part; t < TT; t += ES) {   // the parts share the group's tokens for the softmax
     const int tok = t0 + t;
     if (tok >= p.S) break;
     float* r = rows + t * E;
@@ -316,33 +326,39 @@ __global__ void __launch_bounds__(1024) router_slots_kernel(const RouterParams p
   if (threadIdx.x == 0) p.expert_counts[e] = base_s;
 }
 
-template <typename T, int TT, int WARPS>
+template <typename T, int TT, int TG, int ES>
 cudaError_t launch_topk_eg(const RouterParams& p, cudaStream_t stream) {
-  const int ctas = (p.S + WARPS * TT - 1) / (WARPS * TT);
+  const int ctas = (p.S + TG * TT - 1) / (TG * TT);
   auto go = [&](auto kern, int eg) -> cudaError_t {
-    const size_t rows = (static_cast<size_t>(WARPS) * TT * p.E * sizeof(float) + 15) & ~size_t(15);
+    const size_t rows = (static_cast<size_t>(TG) * TT * p.E * sizeof(float) + 15) & ~size_t(15);
     const size_t smem = rows + 2 * static_cast<size_t>(eg) * 256 * sizeof(T);
     if (smem > 48 * 1024) {
       cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                            static_cast<int>(smem));
       if (e != cudaSuccess) return e;
     }
-    kern<<<ctas, WARPS * 32, smem, stream>>>(p);
+    kern<<<ctas, TG * ES * 32, smem, stream>>>(p);
     ++g_launches;
     return cudaGetLastError();
   };
-  if (p.E % 32 == 0) return go(router_topk_kernel<T, TT, 32, WARPS>, 32);
-  if (p.E % 16 == 0) return go(router_topk_kernel<T, TT, 16, WARPS>, 16);
-  return go(router_topk_kernel<T, TT, 8, WARPS>, 8);
+  if (p.E % 32 == 0) return go(router_topk_kernel<T, TT, 32, TG, ES>, 32);
+  if (p.E % 16 == 0) return go(router_topk_kernel<T, TT, 16, TG, ES>, 16);
+  return go(router_topk_kernel<T, TT, 8, TG, ES>, 8);
 }
 
-// Tokens per CTA = WARPS * TT: the largest that still gives about one CTA per SM.
+// Tokens per CTA = TG * TT: the largest that still gives about one CTA per SM.  With many
+// experts the experts of a group are split over ES = 4 warps per token group.
 template <typename T>
 cudaError_t launch_topk(const RouterParams& p, cudaStream_t stream) {
-  if (p.S >= 120 * 32) return launch_topk_eg<T, 4, 8>(p, stream);
-  if (p.S >= 120 * 16) return launch_topk_eg<T, 4, 4>(p, stream);
-  if (p.S >= 120 * 8) return launch_topk_eg<T, 2, 4>(p, stream);
-  return launch_topk_eg<T, 1, 4>(p, stream);
+  if (p.E >= 64) {
+    if (p.S >= 120 * 16) return launch_topk_eg<T, 4, 4, 4>(p, stream);
+    if (p.S >= 120 * 8) return launch_topk_eg<T, 2, 4, 4>(p, stream);
+    return launch_topk_eg<T, 1, 4, 4>(p, stream);
+  }
+  if (p.S >= 120 * 32) return launch_topk_eg<T, 4, 8, 1>(p, stream);
+  if (p.S >= 120 * 16) return launch_topk_eg<T, 4, 4, 1>(p, stream);
+  if (p.S >= 120 * 8) return launch_topk_eg<T, 2, 4, 1>(p, stream);
+  return launch_topk_eg<T, 1, 4, 1>(p, stream);
 }
 
 }  // namespace
