@@ -932,8 +932,9 @@ __device__ __forceinline__ void moe_forward_body(const MoeParams& p, const TmaMa
 #pragma unroll
             for (int i = 0; i < kPer; ++i) acc[u][i] = 0.0f;
           for (int j = 0; j < p.k; ++j) {
-            const float wj = __shfl_sync(0xffffffffu, mine.weight, j);
+            // (no warp shuffle here: with H < 256 only some lanes run this loop)
             if (!((live >> j) & 1u)) continue;
+            const float wj = p.routes[static_cast<size_t>(tkn) * p.k + j].weight;
             const uint4* src = ret + (static_cast<size_t>(tkn) * p.k + j) * vecs;
             uint4 x[2];
 #pragma unroll

@@ -28,7 +28,7 @@ struct SpinGuard {
   // returns true when the caller must stop waiting
   __device__ __forceinline__ bool expired(const volatile uint32_t* abort_word,
                                           long long limit = 4000000000LL) {
-    if ((++polls & 0x3FF) != 0) return false;
+    if ((++polls & 0x1F) != 0) return false;   // a poll may itself block for a while (try_wait)
     if (abort_word != nullptr && *abort_word != 0) return true;
     return (clock_now() - start) > limit;
   }
