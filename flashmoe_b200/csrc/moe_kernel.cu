@@ -931,26 +931,41 @@ __device__ __forceinline__ void moe_forward_body(const MoeParams& p, const TmaMa
           for (int u = 0; u < 2; ++u)
 #pragma unroll
             for (int i = 0; i < kPer; ++i) acc[u][i] = 0.0f;
-          for (int j = 0; j < p.k; ++j) {
-            // (no warp shuffle here: with H < 256 only some lanes run this loop)
-            if (!((live >> j) & 1u)) continue;
-            const float wj = p.routes[static_cast<size_t>(tkn) * p.k + j].weight;
-            const uint4* src = ret + (static_cast<size_t>(tkn) * p.k + j) * vecs;
-            uint4 x[2];
+          // rows of four choices are fetched together (eight loads in flight per lane), then
+          // accumulated in choice order.  (No warp shuffle in here: with H < 256 only some lanes
+          // run this loop.)
+          for (int j0 = 0; j0 < p.k; j0 += 4) {
+            uint4 x[4][2];
+            float wj[4];
 #pragma unroll
-            for (int u = 0; u < 2; ++u) if (v0 + 32 * u < vecs) x[u] = __ldcg(src + v0 + 32 * u);
+            for (int jj = 0; jj < 4; ++jj) {
+              const int j = j0 + jj;
+              wj[jj] = 0.0f;
+              if (j < p.k && ((live >> j) & 1u)) {
+                wj[jj] = p.routes[static_cast<size_t>(tkn) * p.k + j].weight;
+                const uint4* src = ret + (static_cast<size_t>(tkn) * p.k + j) * vecs;
 #pragma unroll
-            for (int u = 0; u < 2; ++u) {
-              const uint32_t w4[4] = {x[u].x, x[u].y, x[u].z, x[u].w};
-              if constexpr (EB == 2) {
+                for (int u = 0; u < 2; ++u) if (v0 + 32 * u < vecs) x[jj][u] = __ldcg(src + v0 + 32 * u);
+              }
+            }
 #pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                  acc[u][2 * i] = __fadd_rn(acc[u][2 * i], __fmul_rn(Cvt<T>::up(w4[i] & 0xffffu), wj));
-                  acc[u][2 * i + 1] = __fadd_rn(acc[u][2 * i + 1], __fmul_rn(Cvt<T>::up(w4[i] >> 16), wj));
+            for (int jj = 0; jj < 4; ++jj) {
+              const int j = j0 + jj;
+              if (!(j < p.k && ((live >> j) & 1u))) continue;
+#pragma unroll
+              for (int u = 0; u < 2; ++u) {
+                const uint32_t w4[4] = {x[jj][u].x, x[jj][u].y, x[jj][u].z, x[jj][u].w};
+                if constexpr (EB == 2) {
+#pragma unroll
+                  for (int i = 0; i < 4; ++i) {
+                    acc[u][2 * i] = __fadd_rn(acc[u][2 * i], __fmul_rn(Cvt<T>::up(w4[i] & 0xffffu), wj[jj]));
+                    acc[u][2 * i + 1] = __fadd_rn(acc[u][2 * i + 1], __fmul_rn(Cvt<T>::up(w4[i] >> 16), wj[jj]));
+                  }
+                } else {
+#pragma unroll
+                  for (int i = 0; i < 4; ++i)
+                    acc[u][i] = __fadd_rn(acc[u][i], __fmul_rn(__uint_as_float(w4[i]), wj[jj]));
                 }
-              } else {
-#pragma unroll
-                for (int i = 0; i < 4; ++i) acc[u][i] = __fadd_rn(acc[u][i], __fmul_rn(__uint_as_float(w4[i]), wj));
               }
             }
           }
