@@ -302,6 +302,9 @@ int fmoe_ctx_create(const fmoe_model_desc* model, const fmoe_ep_desc* ep, void* 
     const char* force = std::getenv("FMOE_PAIR");
     if (force) p.pair = std::atoi(force) ? 1 : 0;
     g.cta_pairs = p.pair; g.stages = p.pair ? 6 : 4;
+    p.g1_mode = 0;   // half-width GEMM1 tickets measured no faster on one GPU; FMOE_G1=1|2 to try
+    const char* g1 = std::getenv("FMOE_G1");
+    if (g1) p.g1_mode = std::atoi(g1);
   }
   p.tiles_n0 = (I + g.tile_n0 - 1) / g.tile_n0;
   p.tiles_n1 = (H + g.tile_n1 - 1) / g.tile_n1;

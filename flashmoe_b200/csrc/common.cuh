@@ -55,6 +55,7 @@ struct MoeParams {
   int gated, act, ab_format;  // ab_format: 0 fp16, 1 bf16 (fp32 layers run as BF16 planes)
   int elem_bytes;             // 2, or 4 for fp32 layers
   int pair;                   // 1: CTA pairs (cta_group::2), 0: every CTA alone
+  int g1_mode;                // GEMM1 half tiles (128 columns): 0 never, 1 in the closing segments, 2 always
   int debug_flags;            // FMOE_DEBUG (environment, read at create): 1 = skip MMAs, 2 = skip loads (timing experiments; results are garbage)
   int tiles_n0, tiles_n1;
   int landing_rows;

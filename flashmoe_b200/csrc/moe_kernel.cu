@@ -62,12 +62,13 @@ struct alignas(64) TmaMaps {
   CUtensorMap down;     // [nLx*H, I]          box 64 x 128
 };
 
-enum : int { kTaskGemm0 = 0, kTaskGemm1 = 1, kTaskStop = 2 };
+enum : int { kTaskGemm0 = 0, kTaskGemm1 = 1, kTaskStop = 2, kSegGemm1Half = 3 };
 
 // What one CTA of a pair does for one ticket: its own M tile (the leader takes the even tile of
 // the group, the follower the odd one) of the pair's 256 x 256 output tile.
 struct Task {
   int kind, lx, mt, row0, rows, n, m_in_expert, ticket;
+  int col0, ncols;   // GEMM1: first output column and width (256, or 128 for a half tile)
 };
 
 struct Control {
@@ -419,7 +420,7 @@ __device__ __forceinline__ void moe_forward_body(const MoeParams& p, const TmaMa
       tb.send_pref[E] = sp;
       tb.lx_mt0[nLx] = mt;
       ctl->send_rows = sp;
-      ctl->expected_ret = sp * p.tiles_n1;
+      ctl->expected_ret = sp * p.tiles_n1 * 2;   // counted in half tiles (128 columns)
       ctl->lag = nLx;
     }
   }
@@ -443,7 +444,11 @@ __device__ __forceinline__ void moe_forward_body(const MoeParams& p, const TmaMa
       const int s1 = i + lag;
       const int i1 = min(s1, nLx) + i + (s1 < nLx ? 1 : 0);                 // G1(i)
       tb.seg_first[i0] = groups * p.tiles_n0; tb.seg_kind[i0] = kTaskGemm0; tb.seg_lx[i0] = i;
-      tb.seg_first[i1] = groups * p.tiles_n1; tb.seg_kind[i1] = kTaskGemm1; tb.seg_lx[i1] = i;
+      // GEMM1 as half tiles (128 columns): finer tickets where they end the kernel (the segments
+      // emitted after the last GEMM0 segment), or everywhere (g1_mode 2); never in pair mode
+      const bool half = !kPair && (p.g1_mode == 2 || (p.g1_mode == 1 && i >= nLx - lag));
+      tb.seg_first[i1] = groups * p.tiles_n1 * (half ? 2 : 1);
+      tb.seg_kind[i1] = half ? kSegGemm1Half : kTaskGemm1; tb.seg_lx[i1] = i;
     }
   }
   __syncthreads();
@@ -565,8 +570,17 @@ __device__ __forceinline__ void moe_forward_body(const MoeParams& p, const TmaMa
     const int groups = (mts + kGroup - 1) / kGroup;
     t.kind = tb.seg_kind[lo];
     t.lx = lx;
-    t.n = idx / groups;
-    t.m_in_expert = kGroup * (idx - t.n * groups) + static_cast<int>(pair_rank);
+    const int n2 = idx / groups;
+    t.n = n2;
+    t.col0 = n2 * kUmmaN;
+    t.ncols = kUmmaN;
+    if (t.kind == kSegGemm1Half) {
+      t.kind = kTaskGemm1;
+      t.n = n2 >> 1;
+      t.col0 = n2 * (kUmmaN / 2);
+      t.ncols = kUmmaN / 2;
+    }
+    t.m_in_expert = kGroup * (idx - n2 * groups) + static_cast<int>(pair_rank);
     t.mt = tb.lx_mt0[lx] + t.m_in_expert;
     t.row0 = tb.lx_base[lx] + t.m_in_expert * kTileM;
     t.rows = max(0, min(kTileM, tb.lx_rows[lx] - t.m_in_expert * kTileM));   // 0: no such M tile
@@ -647,8 +661,9 @@ __device__ __forceinline__ void moe_forward_body(const MoeParams& p, const TmaMa
           if (p.gated) { brow0 = t.lx * p.I + t.n * 128; brow1 = brow0; }
           else { brow0 = t.lx * p.I + t.n * 256; brow1 = brow0 + 128; }
         } else {
-          brow0 = t.lx * p.H + t.n * 256; brow1 = brow0 + 128;
+          brow0 = t.lx * p.H + t.col0; brow1 = brow0 + 128;
         }
+        const bool half_b = !g0 && t.ncols == kUmmaN / 2;   // only the first 128 rows of the B tile
         const CUtensorMap* map_b = leader ? map_b0 : map_b1;
         const int brow = leader ? brow0 : brow1;
         const int b_plane_rows = g0 ? nLx * p.I : nLx * p.H;   // rows of one BF16 plane of the weights
@@ -671,10 +686,11 @@ __device__ __forceinline__ void moe_forward_body(const MoeParams& p, const TmaMa
               tma_load_2d_pair(sa, map_a, &ctl->full[s], kb * kTileK, t.row0 + pa * p.landing_rows);
               tma_load_2d_pair(sb, map_b, &ctl->full[s], kb * kTileK, brow + pb * b_plane_rows);
             } else {
-              mbar_expect_tx(&ctl->full[s], STAGE);
+              mbar_expect_tx(&ctl->full[s], half_b ? SA + SB / 2 : STAGE);
               tma_load_2d(sa, map_a, &ctl->full[s], kb * kTileK, t.row0 + pa * p.landing_rows);
               tma_load_2d(sb, map_b0, &ctl->full[s], kb * kTileK, brow0 + pb * b_plane_rows);
-              tma_load_2d(sb + SB / 2, map_b1, &ctl->full[s], kb * kTileK, brow1 + pb * b_plane_rows);
+              if (!half_b)
+                tma_load_2d(sb + SB / 2, map_b1, &ctl->full[s], kb * kTileK, brow1 + pb * b_plane_rows);
             }
           }
         }
@@ -695,7 +711,8 @@ __device__ __forceinline__ void moe_forward_body(const MoeParams& p, const TmaMa
     }
   } else if (ctl->ok && warp == 1) {
     if (lane == 0 && leader) {
-      const uint32_t idesc = umma_idesc_f16(Cvt<T>::kFormat, kGroup * kTileM, kUmmaN);
+      const uint32_t idesc_full = umma_idesc_f16(Cvt<T>::kFormat, kGroup * kTileM, kUmmaN);
+      const uint32_t idesc_half = umma_idesc_f16(Cvt<T>::kFormat, kGroup * kTileM, kUmmaN / 2);
       uint32_t fill = 0, tslot = 0, acc_it = 0;
       for (uint32_t it = 0;; ++it, tslot = (tslot + 1) % kTaskSlots) {
         if (!mbar_wait(&ctl->task_full[tslot], (it / kTaskSlots) & 1, p.abort_word)) {
@@ -705,6 +722,7 @@ __device__ __forceinline__ void moe_forward_body(const MoeParams& p, const TmaMa
         mbar_arrive(&ctl->task_empty[tslot]);
         if (t.kind == kTaskStop) break;
         const int nk = (t.kind == kTaskGemm0 ? nk0 : nk1) * kPairs;
+        const uint32_t idesc = (t.kind == kTaskGemm1 && t.ncols == kUmmaN / 2) ? idesc_half : idesc_full;
         const uint32_t buf = acc_it % kBufs;
         if (!mbar_wait_cluster(&ctl->acc_empty[buf], ((acc_it / kBufs) & 1) ^ 1, p.abort_word)) {
           fail(p, FMOE_PHASE_TMEM_EMPTY, t.mt); break;
@@ -851,9 +869,10 @@ __device__ __forceinline__ void moe_forward_body(const MoeParams& p, const TmaMa
         const int src = static_cast<int>(meta >> kMetaSrcShift);
         const uint32_t ret_row = meta & ((1u << kMetaSrcShift) - 1);
         char* orow = p.peers[valid ? src : p.rank] + p.lay.ret + static_cast<size_t>(ret_row) * p.H * EB;
-        const int col_base = t.n * 256;
+        const int col_base = t.col0;
+        const int chunks = t.ncols / 32;
 #pragma unroll 1
-        for (int c = 0; c < 8; ++c) {
+        for (int c = 0; c < chunks; ++c) {
           uint32_t a[32];
           __syncwarp();
           tmem_ld_32x32(taddr + c * 32, a);
@@ -865,7 +884,7 @@ __device__ __forceinline__ void moe_forward_body(const MoeParams& p, const TmaMa
 #pragma unroll
             for (int i = 0; i < 32; ++i) a[i] = __float_as_uint(__uint_as_float(a[i]) + __uint_as_float(ca[i]));
           }
-          if (c == 7) release_acc();
+          if (c == chunks - 1) release_acc();
           const int col0 = col_base + c * 32;
           if (valid && col0 < p.H) {
             float o[32];
@@ -881,7 +900,7 @@ __device__ __forceinline__ void moe_forward_body(const MoeParams& p, const TmaMa
           const unsigned b = __ballot_sync(0xffffffffu, valid && src == s);
           if (lane == 0 && b != 0)
             red_add_release_sys(reinterpret_cast<uint32_t*>(p.peers[s] + p.lay.ret_arrived),
-                                static_cast<uint32_t>(__popc(b)));
+                                static_cast<uint32_t>(__popc(b)) * static_cast<uint32_t>(t.ncols / 128));
         }
       }
       ++acc_it;

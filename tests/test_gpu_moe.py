@@ -74,6 +74,46 @@ def test_cta_pair_form_of_the_gemm_loop(name, monkeypatch):
         layer.close()
 
 
+@pytest.mark.parametrize("mode", ["1", "2"])
+def test_half_width_gemm1_tickets(mode, monkeypatch):
+    """FMOE_G1 = 1 / 2 cuts the closing / all GEMM1 tickets into 128-column halves."""
+    monkeypatch.setenv("FMOE_G1", mode)
+    w = GOLDEN_CASES["bf16_two_mtiles"].scaled(token_dim=512)
+    lw, x = make_weights(w), make_tokens(w)
+    ref, _ = oracle_layer(w, x=x, lw=lw)
+    layer = make_layer(w, lw)
+    try:
+        for _ in range(2):
+            assert max_rel_err(layer.forward(x).cpu(), ref) <= 2e-2
+    finally:
+        layer.close()
+
+
+def test_forwards_replay_from_a_cuda_graph():
+    """The reference times its kernel by capturing many forwards in one CUDA graph and replaying
+    it (quickstart.py:264-291).  Nothing on the host changes between launches here either: the
+    epoch lives in device memory."""
+    w = GOLDEN_CASES["bf16_gated_k2"]
+    lw, x = make_weights(w), make_tokens(w)
+    ref, _ = oracle_layer(w, x=x, lw=lw)
+    layer = make_layer(w, lw)
+    try:
+        layer.forward(x)                      # warm-up outside the capture, routes the tokens
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=layer.stream):
+            for _ in range(4):
+                layer.experts()
+        layer.out.zero_()
+        for _ in range(3):
+            with torch.cuda.stream(layer.stream):
+                g.replay()
+        layer.stream.synchronize()
+        layer.check()
+        assert max_rel_err(layer.out.cpu(), ref) <= 2e-2
+    finally:
+        layer.close()
+
+
 def test_stages_dispatch_gemm0_gemm1():
     """Checks the intermediate buffers: landed rows (exact), GEMM0 output and returned rows."""
     w = GOLDEN_CASES["bf16_gated_k2"]
