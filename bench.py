@@ -161,6 +161,9 @@ def main() -> int:
     ap.add_argument("--tokens", type=int, default=None, help="override tokens_per_rank")
     ap.add_argument("--impl", default="flashmoe_b200", choices=["flashmoe_b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--capacity", default="nodrop", choices=["nodrop", "reference"],
+                    help="expert_peer_capacity: tokens_per_rank (nothing dropped, default) or the "
+                         "reference's default ceil(S/E)*k (tokens beyond it are dropped)")
     a = ap.parse_args()
 
     import torch
@@ -176,12 +179,15 @@ def main() -> int:
     w = CONFIGS[a.workload]
     if a.tokens:
         w = w.scaled(tokens_per_rank=a.tokens)
+    if a.capacity == "reference":
+        w = w.scaled(capacity=w.reference_default_capacity)
     a.warmup = max(a.warmup, 3)
     S, H, I, E, k = w.tokens_per_rank, w.token_dim, w.ffn_size, w.num_experts, w.top_k
     eb = 2
     cfg = {"workload": f"{w.name}: tokens_per_rank={S} H={H} I={I} E={E} k={k} "
                        f"{'gated' if w.mlp_type == MLPType.GATED else 'plain'} {w.act_type.name} "
-                       f"{w.data_type.name}, expert_peer_capacity={w.expert_peer_capacity} (no drop)",
+                       f"{w.data_type.name}, expert_peer_capacity={w.expert_peer_capacity} "
+                       f"({'no drop' if a.capacity == 'nodrop' else 'reference default, drops'})",
            "parallelism": f"ep{world}xdp{world}", "experts_per_gpu": E // world,
            "step": "router (2 launches) + fused dispatch/experts/combine (1 launch)"}
     dev = torch.device("cuda", local_rank)
