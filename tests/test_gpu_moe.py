@@ -195,6 +195,86 @@ def test_benchmark_shapes_trimmed_tokens(cfg, S):
         layer.close()
 
 
+@pytest.mark.parametrize("S", [1, 16])
+def test_qwen3_decode_sizes(S):
+    """The decode end of the Qwen3-30B-A3B sweep (1 and 16 tokens, E = 128, k = 8)."""
+    w = CONFIGS["qwen3"].scaled(tokens_per_rank=S)
+    lw, x = make_weights(w), make_tokens(w)
+    ref, _ = oracle_layer(w, x=x, lw=lw)
+    layer = make_layer(w, lw)
+    try:
+        for _ in range(2):
+            out = layer.forward(x).cpu()
+            assert max_rel_err(out, ref) <= 2e-2, max_rel_err(out, ref)
+    finally:
+        layer.close()
+
+
+def test_qwen3_fp32_plain_gelu():
+    """The FP32 leg of the Qwen3 sweep: plain (non-gated) MLP with GELU, 16 tokens, all 128 experts'
+    shapes; tolerance 1e-5."""
+    w = CONFIGS["qwen3_fp32_gelu"].scaled(tokens_per_rank=16)
+    lw, x = make_weights(w), make_tokens(w)
+    ref, _ = oracle_layer(w, x=x, lw=lw)
+    layer = make_layer(w, lw)
+    try:
+        out = layer.forward(x).cpu()
+        assert max_rel_err(out, ref) <= 1e-5, max_rel_err(out, ref)
+    finally:
+        layer.close()
+
+
+def _device_layer(w):
+    """Layer with weights drawn on the GPU (full-size configurations: tens of GB would take minutes
+    to draw on the host)."""
+    import importlib.util
+    import os
+    from flashmoe_b200.layer import MoELayer
+    spec = importlib.util.spec_from_file_location(
+        "bench", os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "bench.py"))
+    bench = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(bench)
+    lw = bench.device_weights(w, torch.device("cuda", 0), list(range(w.num_experts)))
+    return MoELayer(w, lw, 0, local_experts=range(w.num_experts)), lw
+
+
+@pytest.mark.parametrize("cfg,S", [("mixtral", 4096), ("deepseek_v3", 2048), ("qwen3", 8192)])
+def test_full_size_properties(cfg, S):
+    """Mixtral, DeepSeek-V3-shaped and Qwen3 (prefill end) at their full benchmark sizes, through
+    properties that need no full-size oracle: finite output, determinism across launches, bit-exact
+    equivariance under a permutation of the tokens, and a handful of tokens against the oracle
+    (only the experts those tokens use are copied to the host)."""
+    w = CONFIGS[cfg].scaled(tokens_per_rank=S)
+    layer, lw = _device_layer(w)
+    try:
+        x = make_tokens(w)
+        out = layer.forward(x).cpu()
+        assert torch.isfinite(out.float()).all()
+        again = layer.forward(x).cpu()
+        assert torch.equal(out, again)
+        perm = torch.randperm(S, generator=torch.Generator().manual_seed(9))
+        outp = layer.forward(x[perm]).cpu()
+        assert torch.equal(outp, out[perm])
+        # spot tokens: route them with the oracle, run their experts on the host
+        sel = torch.arange(0, S, S // 6)[:6]
+        bias = None if lw.logit_bias is None else lw.logit_bias.cpu().numpy()
+        r = O.route(x[sel].float().numpy(), lw.router.cpu().float().numpy(), w.top_k, len(sel), logit_bias=bias)
+        for i, t in enumerate(sel.tolist()):
+            acc = torch.zeros(w.token_dim)
+            for j in range(w.top_k):
+                e = int(r.topk_idx[i, j])
+                one = O.ExpertWeights(lw.up[e:e + 1].cpu(), None if lw.up_v is None else lw.up_v[e:e + 1].cpu(),
+                                      lw.down[e:e + 1].cpu(), lw.bias_up[e:e + 1].cpu(),
+                                      None if lw.bias_up_v is None else lw.bias_up_v[e:e + 1].cpu(),
+                                      lw.bias_down[e:e + 1].cpu())
+                _, o = O.expert_mlp(x[t:t + 1], one, 0, int(w.mlp_type), int(w.act_type))
+                acc = o[0].float() if w.top_k == 1 else acc + o[0].float() * float(r.topk_w[i, j])
+            ref_t = acc.to(out.dtype)
+            assert max_rel_err(out[t], ref_t) <= 2e-2, (t, max_rel_err(out[t], ref_t))
+    finally:
+        layer.close()
+
+
 def test_full_size_scout_properties():
     """Scout at its full benchmark size (S = 1024, H = 5120, I = 8192, E = 16, k = 1), checked
     through properties that need no full-size oracle: (1) determinism across launches, (2) a
