@@ -167,7 +167,7 @@ def main() -> int:
     a = ap.parse_args()
 
     import torch
-    from flashmoe_b200.workloads import CONFIGS, flops_per_rank, make_tokens, weight_bytes_per_rank
+    from flashmoe_b200.workloads import CONFIGS, make_tokens, weight_bytes_per_rank
     from flashmoe_b200.jit import MLPType
 
     rank = int(os.environ.get("RANK", "0"))
@@ -334,6 +334,18 @@ def main() -> int:
                 "t_tensor_us": t_tensor * 1e6, "t_hbm_us": t_hbm * 1e6,
                 "pct_dense_bf16_peak_burst": 100.0 * flops / sec_kernel / (peaks["bf16_tflops"] * 1e12)}
 
+    # --- NVLink: bytes this rank pushed to other GPUs during the dispatch phase -------------------
+    nvlink = None
+    if world > 1:
+        remote_rows = sum(min(counts[e], cap) for e in range(E) if e not in mine)
+        out_bytes = float(remote_rows) * H * eb
+        nvlink = {"dispatch_bytes_out": out_bytes, "return_bytes_in": out_bytes,
+                  "dispatch_us": phases["dispatch"],
+                  "dispatch_gbs": out_bytes / max(phases["dispatch"], 1e-9) / 1e3,
+                  "peak_nominal_gbs": 900.0, "peak_measured_peer_copy_gbs": 770.0,
+                  "note": "rank 0, per direction; the dispatch phase also copies the local rows; "
+                          "returned rows travel during the GEMM phase (GEMM1 epilogues store them remotely)"}
+
     # --- CPU baseline on a bounded sample (rank 0, N = 1 only) ----------------------------------
     cpu = None
     if rank == 0 and world == 1 and not a.no_cpu_baseline:
@@ -367,7 +379,7 @@ def main() -> int:
             "e2e": {"value": tokens_job / e2e_s, "unit": "tokens/s", "ms_per_step": e2e_s * 1e3,
                     "h2d_bytes_per_step": S * H * eb, "d2h_bytes_per_step": S * H * eb,
                     "api": "fmoe_forward_host (C ABI, pinned host buffers)"},
-            "gpu_launches": int(launches), "phases_us": phases, "roofline": roofline, "cpu_baseline": cpu, "clocks": clocks}
+            "gpu_launches": int(launches), "phases_us": phases, "nvlink": nvlink, "roofline": roofline, "cpu_baseline": cpu, "clocks": clocks}
     print(json.dumps(line))
     return 0
 

@@ -310,7 +310,8 @@ __device__ __forceinline__ void moe_forward_body(const MoeParams& p, const TmaMa
   if constexpr (kPair) cluster_sync_all();   // the peer's barriers exist before anything arrives on them
   tc_fence_after_sync();
   // per-CTA phase stamps (%globaltimer, ns): 0 start, 1 counts of all ranks in, 2 tables built,
-  // 3 dispatch done, 4 first ticket drawn, 5 last ticket (stop) seen, 6 returns all in, 7 combine done
+  // 3 dispatch done, 4 last ticket (stop) drawn, 5 this CTA's last task finished, 6 returns all in,
+  // 7 combine done
   auto stamp = [&](int i) {
     if (tid == 0) {
       unsigned long long t;
@@ -593,7 +594,6 @@ __device__ __forceinline__ void moe_forward_body(const MoeParams& p, const TmaMa
       uint32_t fill = 0;  // stage fills issued so far
       uint32_t tslot = 0;
       bool ok = true;
-      stamp(4);
       for (uint32_t it = 0; ok; ++it, tslot = (tslot + 1) % kTaskSlots) {
         const uint32_t ring_par = (it / kTaskSlots) & 1;
         int ticket;
@@ -646,7 +646,7 @@ __device__ __forceinline__ void moe_forward_body(const MoeParams& p, const TmaMa
         }
         ctl->tasks[tslot] = t;
         mbar_arrive(&ctl->task_full[tslot]);
-        if (t.kind == kTaskStop) { stamp(5); break; }
+        if (t.kind == kTaskStop) { stamp(4); break; }
         fence_proxy_async();
 
         const bool g0 = t.kind == kTaskGemm0;
@@ -911,6 +911,7 @@ __device__ __forceinline__ void moe_forward_body(const MoeParams& p, const TmaMa
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
+  stamp(5);
   if (tid == 0 && ctl->ok && *reinterpret_cast<volatile uint32_t*>(p.abort_word) == 0) {
     const uint32_t* ra = reinterpret_cast<const uint32_t*>(self + p.lay.ret_arrived);
     if (!wait_counter_sys(ra, static_cast<uint32_t>(ctl->expected_ret), p)) {

@@ -112,19 +112,18 @@ class MoELayer:
         assert nbytes <= n
         return raw[:nbytes].view(dtype).reshape(shape).clone()
 
-    PHASES = ("count_exchange", "tables", "dispatch", "gemm_tasks", "wait_returns", "combine")
-
     def phases(self) -> dict:
         """Per-phase times of the LAST forward from the kernel's per-CTA %globaltimer stamps, in
         microseconds: median over CTAs for each phase, the whole kernel (first start to last end),
         and the share of the kernel a median CTA spent in communication it could not overlap
-        (count exchange + dispatch + waiting for returned rows)."""
+        (count exchange + dispatch + waiting, after its own last task, for returned rows)."""
         g = self.geometry()
         t = self.debug(5, torch.int64, (g.grid, 8)).cpu().double()
         d = (t[:, 1:] - t[:, :-1]) / 1e3
         med = d.median(dim=0).values
         out = {"count_exchange": float(med[0]), "tables": float(med[1]), "dispatch": float(med[2]),
-               "gemm_tasks": float(med[4]), "wait_returns": float(med[5]), "combine": float(med[6]),
+               "gemm_tickets": float(med[3]), "drain_last_task": float(med[4]),
+               "wait_returns": float(med[5]), "combine": float(med[6]),
                "kernel": float((t[:, 7].max() - t[:, 0].min()) / 1e3)}
         out["exposed_comm_frac"] = (out["count_exchange"] + out["dispatch"] + out["wait_returns"]) / \
             max(out["kernel"], 1e-9)

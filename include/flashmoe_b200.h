@@ -207,8 +207,8 @@ int fmoe_get_geometry(const fmoe_ctx* ctx, fmoe_geometry* out);
  *        2 GEMM0 output [landing_rows, I], 3 return rows [S*k, H],
  *        4 route records [S, k] of {int32 expert, int32 slot, float weight},
  *        5 phase stamps of the last forward: uint64 [grid][8] %globaltimer nanoseconds per CTA
- *          (0 start, 1 all ranks' counts in, 2 tables built, 3 dispatch done, 4 first ticket,
- *           5 last ticket, 6 all returns in, 7 combine done) */
+ *          (0 start, 1 all ranks' counts in, 2 tables built, 3 dispatch done, 4 last ticket drawn,
+ *           5 this CTA's last task finished, 6 all returns in, 7 combine done) */
 int fmoe_debug_buffer(fmoe_ctx* ctx, int32_t which, void** ptr_out, size_t* bytes_out);
 
 #ifdef __cplusplus
