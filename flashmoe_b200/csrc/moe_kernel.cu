@@ -594,11 +594,13 @@ __device__ __forceinline__ void moe_forward_body(const MoeParams& p, const TmaMa
       uint32_t fill = 0;  // stage fills issued so far
       uint32_t tslot = 0;
       bool ok = true;
+      int next_ticket = -1;   // drawn a few K blocks before the current task's loads end
       for (uint32_t it = 0; ok; ++it, tslot = (tslot + 1) % kTaskSlots) {
         const uint32_t ring_par = (it / kTaskSlots) & 1;
         int ticket;
         if (leader) {
-          ticket = static_cast<int>(atomicAdd(p.ticket, 1u));
+          ticket = next_ticket >= 0 ? next_ticket : static_cast<int>(atomicAdd(p.ticket, 1u));
+          next_ticket = -1;
         } else {
           if (!mbar_wait_cluster(&ctl->pair_full[tslot], ring_par, p.abort_word)) {
             fail(p, FMOE_PHASE_TASK, -3); ok = false; break;
@@ -668,6 +670,10 @@ __device__ __forceinline__ void moe_forward_body(const MoeParams& p, const TmaMa
         const int brow = leader ? brow0 : brow1;
         const int b_plane_rows = g0 ? nLx * p.I : nLx * p.H;   // rows of one BF16 plane of the weights
         for (int kb = 0; kb < nk && ok; ++kb) {
+          // the next ticket is drawn while the last stages of this task are still being consumed,
+          // so the atomic's round trip is off the path between two tasks (not earlier: a CTA
+          // holding a spare ticket for long would unbalance the closing wave)
+          if (leader && kb == max(0, nk - 6)) next_ticket = static_cast<int>(atomicAdd(p.ticket, 1u));
           for (int pp = 0; pp < kPairs; ++pp, ++fill) {
             const int pa = kPlanes == 1 ? 0 : kPairA[pp], pb = kPlanes == 1 ? 0 : kPairB[pp];
             const uint32_t s = fill % NS;
