@@ -10,6 +10,10 @@ if ROOT not in sys.path:
 
 def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: needs a CUDA device (B200, sm_100a)")
+    # the tests go through the in-tree shared library; build it if this checkout has none yet
+    from flashmoe_b200 import _native
+    if not _native.LIB_PATH.exists():
+        _native.build()
 
 
 def pytest_collection_modifyitems(config, items):
