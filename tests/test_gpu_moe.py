@@ -102,7 +102,7 @@ def test_forwards_replay_from_a_cuda_graph():
         g = torch.cuda.CUDAGraph()
         with torch.cuda.graph(g, stream=layer.stream):
             for _ in range(4):
-                layer.experts()
+                layer.step()             # router (2 launches) + fused forward
         layer.out.zero_()
         for _ in range(3):
             with torch.cuda.stream(layer.stream):
