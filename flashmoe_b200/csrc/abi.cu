@@ -284,6 +284,11 @@ int fmoe_ctx_create(const fmoe_model_desc* model, const fmoe_ep_desc* ep, void* 
   if (ce == cudaSuccess) ce = cudaMemcpyAsync(c->work + w_local, c->local_e.data(), sizeof(int32_t) * W * nLx, cudaMemcpyHostToDevice, st);
   if (ce == cudaSuccess) ce = cudaStreamSynchronize(st);
   if (ce == cudaSuccess) ce = moe_prepare_kernel(g.smem_bytes);
+  if (ce == cudaSuccess) {
+    // every device-side wait gives up after this long (default 2 s; FMOE_SPIN_LIMIT_MS overrides)
+    const char* lim = std::getenv("FMOE_SPIN_LIMIT_MS");
+    ce = set_spin_limit_ms(lim ? std::atof(lim) : 2000.0);
+  }
   if (ce != cudaSuccess) { free_ctx(c); return set_error(FMOE_ERR_CUDA, std::string("workspace set-up: ") + cudaGetErrorString(ce)); }
 
   MoeParams& p = c->params;

@@ -56,7 +56,7 @@ struct MoeParams {
   int elem_bytes;             // 2, or 4 for fp32 layers
   int pair;                   // 1: CTA pairs (cta_group::2), 0: every CTA alone
   int g1_mode;                // GEMM1 half tiles (128 columns): 0 never, 1 in the closing segments, 2 always
-  int debug_flags;            // FMOE_DEBUG (environment, read at create): 1 = skip MMAs, 2 = skip loads (timing experiments; results are garbage)
+  int debug_flags;            // FMOE_DEBUG (environment, read at create): 1 = skip MMAs, 2 = skip loads (timing experiments; results are garbage), 4 = withhold the count flags (makes the first wait run out)
   int tiles_n0, tiles_n1;
   int landing_rows;
   int max_mtiles;
@@ -108,6 +108,7 @@ struct RouterParams {
 cudaError_t launch_router(const RouterParams& p, cudaStream_t stream);
 size_t moe_smem_bytes(int W, int E, int nLx);
 cudaError_t moe_prepare_kernel(size_t smem);
+cudaError_t set_spin_limit_ms(double ms);   // bound of every device-side wait, this device
 cudaError_t launch_split_planes(const float* in, void* out, size_t n, cudaStream_t stream);
 cudaError_t launch_moe(const MoeParams& p, const CUtensorMap* maps, int grid, size_t smem,
                        cudaStream_t stream);

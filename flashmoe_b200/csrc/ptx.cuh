@@ -21,16 +21,17 @@ __device__ __forceinline__ long long clock_now() {
   asm volatile("mov.u64 %0, %%clock64;" : "=l"(t));
   return t;
 }
+// How long a wait may last, in SM clock ticks (set from the host when a context is created).
+__device__ long long g_spin_limit_cycles = 4000000000LL;
 struct SpinGuard {
   long long start;
   uint32_t polls;
   __device__ __forceinline__ SpinGuard() : polls(0) { start = clock_now(); }
   // returns true when the caller must stop waiting
-  __device__ __forceinline__ bool expired(const volatile uint32_t* abort_word,
-                                          long long limit = 4000000000LL) {
+  __device__ __forceinline__ bool expired(const volatile uint32_t* abort_word) {
     if ((++polls & 0x1F) != 0) return false;   // a poll may itself block for a while (try_wait)
     if (abort_word != nullptr && *abort_word != 0) return true;
-    return (clock_now() - start) > limit;
+    return (clock_now() - start) > g_spin_limit_cycles;
   }
 };
 

@@ -316,6 +316,34 @@ def test_host_buffer_entry_point():
         layer.close()
 
 
+def test_a_wait_that_runs_out_is_reported_and_the_gpu_stays_usable(monkeypatch):
+    """Failure detection without a fault: the count flags are withheld (nothing ever sets what the
+    first wait polls), the wait gives up after its limit, the kernel leaves through its common
+    exit and the host reads {code, phase} from the status record.  A fresh context then works."""
+    import flashmoe_b200 as flashmoe
+    w = GOLDEN_CASES["bf16_gated_k2"]
+    lw, x = make_weights(w), make_tokens(w)
+    monkeypatch.setenv("FMOE_DEBUG", "4")
+    monkeypatch.setenv("FMOE_SPIN_LIMIT_MS", "20")
+    layer = make_layer(w, lw)
+    try:
+        with pytest.raises(flashmoe.FlashMoEError) as err:
+            layer.forward(x)
+        assert err.value.code == 5 and "phase 1" in str(err.value)      # DEVICE_TIMEOUT in the count wait
+        st = layer.handle.mod.last_status(layer.handle.context, layer.stream.cuda_stream)
+        assert (st.code, st.phase, st.rank) == (5, 1, 0)
+    finally:
+        layer.close()
+    monkeypatch.delenv("FMOE_DEBUG")
+    monkeypatch.delenv("FMOE_SPIN_LIMIT_MS")
+    ref, _ = oracle_layer(w, x=x, lw=lw)
+    layer = make_layer(w, lw)
+    try:
+        assert max_rel_err(layer.forward(x).cpu(), ref) <= 2e-2
+    finally:
+        layer.close()
+
+
 def test_argument_errors_are_reported_not_fatal():
     import flashmoe_b200 as flashmoe
     w = GOLDEN_CASES["bf16_gated_k2"]
