@@ -120,6 +120,35 @@ def test_two_rank_exchange_matches_single_rank_oracle(name):
         assert err < 1e-6, (rank, err)
 
 
+def _failing_peer(rank, world, port, q):
+    import datetime
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=10))
+    cb.initialize()
+    if rank == 1:
+        os._exit(0)          # leaves before the handle exchange, with nothing in flight
+    try:
+        cb.all_gather_bytes(b"x" * 64)
+        q.put("no error")
+    except Exception as exc:  # the survivor learns of it on the host, before any launch
+        q.put("error: " + type(exc).__name__)
+    os._exit(0)
+
+
+def test_a_rank_that_leaves_before_the_handle_exchange_is_noticed_on_the_host():
+    import socket
+    s = socket.socket(); s.bind(("127.0.0.1", 0)); port = s.getsockname()[1]; s.close()
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_failing_peer, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    msg = q.get(timeout=60)
+    for p in procs:
+        p.join(timeout=30)
+    assert msg.startswith("error"), msg
+
+
 def test_layout_matches_hand_computed_example():
     counts = [[3, 0, 130, 1], [2, 5, 0, 200]]
     lay = layout.build(counts, 1, [0, 0, 1, 1], ec=128, tiles_n0=2, tiles_n1=1, grid=1)
