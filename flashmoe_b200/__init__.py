@@ -90,17 +90,20 @@ class _MoEModule:
         N.check(self._lib.fmoe_debug_buffer(C.c_void_p(raw_ctx), which, C.byref(p), C.byref(n)), "debug_buffer")
         return p.value, n.value
 
+    def forward_host_wait(self, raw_ctx, stream_ptr) -> None:
+        N.check(self._lib.fmoe_forward_host_wait(C.c_void_p(raw_ctx), C.c_void_p(stream_ptr)), "forward_host_wait")
+
     def forward_host(self, raw_ctx, router_ctx, tokens_host, out_host, rargs: "router.RouterForwardArgs",
-                     fargs: ForwardArgs) -> None:
+                     fargs: ForwardArgs, *, wait: bool = True) -> None:
         ra = N.RouterArgsC(0, rargs.weights, rargs.routing or None, rargs.expert_counts,
                            rargs.logit_bias or None)
         fa = N.ForwardArgsC(0, fargs.expert_counts, fargs.local_expert_up, fargs.local_expert_up_v or None,
                             fargs.local_bias_up or None, fargs.local_bias_up_v or None,
                             fargs.local_expert_down, fargs.local_bias_down or None, 0,
                             fargs.swish_alpha, fargs.swish_beta)
-        N.check(self._lib.fmoe_forward_host(C.c_void_p(raw_ctx), C.c_void_p(router_ctx),
-                                            C.c_void_p(tokens_host), C.c_void_p(out_host), C.byref(ra),
-                                            C.byref(fa), C.c_void_p(fargs.stream_ptr)), "forward_host")
+        fn = self._lib.fmoe_forward_host if wait else self._lib.fmoe_forward_host_async
+        N.check(fn(C.c_void_p(raw_ctx), C.c_void_p(router_ctx), C.c_void_p(tokens_host), C.c_void_p(out_host),
+                   C.byref(ra), C.byref(fa), C.c_void_p(fargs.stream_ptr)), "forward_host")
 
 
 def initialize(arg: InitArgs) -> ContextHandle:

@@ -79,6 +79,9 @@ SIGNATURES = {
                                             C.c_void_p, C.c_int32, C.c_void_p, C.c_void_p]),
     "fmoe_forward_host": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
                                     C.POINTER(RouterArgsC), C.POINTER(ForwardArgsC), C.c_void_p]),
+    "fmoe_forward_host_async": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
+                                          C.POINTER(RouterArgsC), C.POINTER(ForwardArgsC), C.c_void_p]),
+    "fmoe_forward_host_wait": (C.c_int, [C.c_void_p, C.c_void_p]),
     "fmoe_last_status": (C.c_int, [C.c_void_p, C.c_void_p, C.POINTER(Status)]),
     "fmoe_strerror": (C.c_char_p, [C.c_int]),
     "fmoe_last_error": (C.c_char_p, []),

@@ -93,6 +93,15 @@ struct fmoe_ctx {
   const void* map_src[3] = {nullptr, nullptr, nullptr};  // up, up_v, down the maps were built for
   void* stage_tokens = nullptr;         // host-buffer entry point staging
   void* stage_out = nullptr;
+  // pipelined host-buffer entry point: two slots, a copy-in and a copy-out stream, events per slot
+  struct Pipe {
+    bool ready = false;
+    cudaStream_t s_in = nullptr, s_out = nullptr;
+    void* tokens[2] = {nullptr, nullptr};
+    void* out[2] = {nullptr, nullptr};
+    cudaEvent_t in_done[2] = {}, compute_done[2] = {}, out_done[2] = {};
+    unsigned long long submitted = 0;
+  } pipe;
   int eb = 2;                           // bytes per Element (4 for fp32 layers)
   int planes = 1;                       // BF16 planes per GEMM operand (3 for fp32 layers)
   char* wsplit = nullptr;               // fp32 layers: BF16 planes of up | up_v | down
@@ -151,6 +160,14 @@ void free_ctx(fmoe_ctx* c) {
   if (c->wsplit) cudaFree(c->wsplit);
   if (c->stage_tokens) cudaFree(c->stage_tokens);
   if (c->stage_out) cudaFree(c->stage_out);
+  if (c->pipe.ready) {
+    for (int i = 0; i < 2; ++i) {
+      cudaFree(c->pipe.tokens[i]); cudaFree(c->pipe.out[i]);
+      cudaEventDestroy(c->pipe.in_done[i]); cudaEventDestroy(c->pipe.compute_done[i]);
+      cudaEventDestroy(c->pipe.out_done[i]);
+    }
+    cudaStreamDestroy(c->pipe.s_in); cudaStreamDestroy(c->pipe.s_out);
+  }
   delete c;
 }
 
@@ -569,6 +586,64 @@ int fmoe_forward_host(fmoe_ctx* ctx, fmoe_router* router, const void* tokens_hos
   if (rc != FMOE_OK) return rc;
   FMOE_CUDA(cudaMemcpyAsync(out_host, ctx->stage_out, bytes, cudaMemcpyDeviceToHost, st));
   FMOE_CUDA(cudaStreamSynchronize(st));
+  return FMOE_OK;
+}
+
+int fmoe_forward_host_async(fmoe_ctx* ctx, fmoe_router* router, const void* tokens_host, void* out_host,
+                            const fmoe_router_args* rargs, const fmoe_forward_args* args, void* stream) {
+  if (ctx == nullptr || router == nullptr || tokens_host == nullptr || out_host == nullptr ||
+      rargs == nullptr || args == nullptr)
+    return set_error(FMOE_ERR_INVALID_ARG, "null argument");
+  const size_t bytes = static_cast<size_t>(ctx->params.S) * ctx->params.H * ctx->eb;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  fmoe_ctx::Pipe& pp = ctx->pipe;
+  if (!pp.ready) {
+    FMOE_CUDA(cudaSetDevice(ctx->device));
+    FMOE_CUDA(cudaStreamCreateWithFlags(&pp.s_in, cudaStreamNonBlocking));
+    FMOE_CUDA(cudaStreamCreateWithFlags(&pp.s_out, cudaStreamNonBlocking));
+    for (int i = 0; i < 2; ++i) {
+      FMOE_CUDA(cudaMalloc(&pp.tokens[i], bytes));
+      FMOE_CUDA(cudaMalloc(&pp.out[i], bytes));
+      FMOE_CUDA(cudaEventCreateWithFlags(&pp.in_done[i], cudaEventDisableTiming));
+      FMOE_CUDA(cudaEventCreateWithFlags(&pp.compute_done[i], cudaEventDisableTiming));
+      FMOE_CUDA(cudaEventCreateWithFlags(&pp.out_done[i], cudaEventDisableTiming));
+    }
+    pp.ready = true;
+  }
+  const int slot = static_cast<int>(pp.submitted & 1);
+  const bool reused = pp.submitted >= 2;   // the slot's previous user is step n - 2
+  // copy-in: the slot's token buffer is free once the kernels of step n - 2 are done
+  if (reused) FMOE_CUDA(cudaStreamWaitEvent(pp.s_in, pp.compute_done[slot], 0));
+  FMOE_CUDA(cudaMemcpyAsync(pp.tokens[slot], tokens_host, bytes, cudaMemcpyHostToDevice, pp.s_in));
+  FMOE_CUDA(cudaEventRecord(pp.in_done[slot], pp.s_in));
+  // kernels: after this step's tokens are in and step n - 2's result has left the slot
+  FMOE_CUDA(cudaStreamWaitEvent(st, pp.in_done[slot], 0));
+  if (reused) FMOE_CUDA(cudaStreamWaitEvent(st, pp.out_done[slot], 0));
+  fmoe_router_args ra = *rargs;
+  ra.tokens = pp.tokens[slot];
+  int rc = fmoe_router_forward(router, ctx, &ra, stream);
+  if (rc != FMOE_OK) return rc;
+  fmoe_forward_args fa = *args;
+  fa.tokens = pp.tokens[slot];
+  fa.moe_out = pp.out[slot];
+  rc = fmoe_forward(ctx, &fa, stream);
+  if (rc != FMOE_OK) return rc;
+  FMOE_CUDA(cudaEventRecord(pp.compute_done[slot], st));
+  // copy-out
+  FMOE_CUDA(cudaStreamWaitEvent(pp.s_out, pp.compute_done[slot], 0));
+  FMOE_CUDA(cudaMemcpyAsync(out_host, pp.out[slot], bytes, cudaMemcpyDeviceToHost, pp.s_out));
+  FMOE_CUDA(cudaEventRecord(pp.out_done[slot], pp.s_out));
+  ++pp.submitted;
+  return FMOE_OK;
+}
+
+int fmoe_forward_host_wait(fmoe_ctx* ctx, void* stream) {
+  if (ctx == nullptr) return set_error(FMOE_ERR_INVALID_ARG, "null context");
+  FMOE_CUDA(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)));
+  if (ctx->pipe.ready) {
+    FMOE_CUDA(cudaStreamSynchronize(ctx->pipe.s_in));
+    FMOE_CUDA(cudaStreamSynchronize(ctx->pipe.s_out));
+  }
   return FMOE_OK;
 }
 

@@ -84,10 +84,15 @@ class MoELayer:
         self.check()
         return self.out.clone()
 
-    def forward_host(self, tokens_host: torch.Tensor, out_host: torch.Tensor) -> None:
-        """Host buffers in, host buffers out, through the C ABI's fmoe_forward_host."""
+    def forward_host(self, tokens_host: torch.Tensor, out_host: torch.Tensor, wait: bool = True) -> None:
+        """Host buffers in, host buffers out, through the C ABI's fmoe_forward_host (wait=True) or
+        its pipelined form fmoe_forward_host_async (wait=False; call host_wait() at the end)."""
         self.handle.mod.forward_host(self.handle.context, self.router_handle.context,
-                                     tokens_host.data_ptr(), out_host.data_ptr(), self.rargs, self.fargs)
+                                     tokens_host.data_ptr(), out_host.data_ptr(), self.rargs, self.fargs,
+                                     wait=wait)
+
+    def host_wait(self) -> None:
+        self.handle.mod.forward_host_wait(self.handle.context, self.stream.cuda_stream)
 
     def check(self) -> None:
         st = self.handle.mod.last_status(self.handle.context, self.stream.cuda_stream)

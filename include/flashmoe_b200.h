@@ -179,6 +179,18 @@ int fmoe_forward_host(fmoe_ctx* ctx, fmoe_router* router, const void* tokens_hos
                       void* out_host, const fmoe_router_args* rargs,
                       const fmoe_forward_args* args, void* stream);
 
+/* The same step without waiting for it: the copy-in of step n runs on a stream of its own and
+ * overlaps the kernels of step n - 1, the copy-out overlaps the kernels of step n + 1 (two
+ * staging slots; `tokens_host` may be reused once the call returns only if it is not rewritten
+ * before the copy-in ran, so alternate two host buffers; `out_host` holds step n's result after
+ * fmoe_forward_host_wait, or once two later steps have been submitted and waited for).
+ * The kernels run on `stream`; every rank must submit the same number of steps. */
+int fmoe_forward_host_async(fmoe_ctx* ctx, fmoe_router* router, const void* tokens_host,
+                            void* out_host, const fmoe_router_args* rargs,
+                            const fmoe_forward_args* args, void* stream);
+/* Blocks until every submitted step, its copies included, is done. */
+int fmoe_forward_host_wait(fmoe_ctx* ctx, void* stream);
+
 /* --- diagnostics --------------------------------------------------------------------- */
 
 /* Reads the record the last forward left (synchronises `stream` first). */

@@ -344,6 +344,26 @@ def test_a_wait_that_runs_out_is_reported_and_the_gpu_stays_usable(monkeypatch):
         layer.close()
 
 
+def test_pipelined_host_buffer_entry_point():
+    """fmoe_forward_host_async: five steps with different tokens, copies overlapping kernels; every
+    step's result must land in its own host buffer."""
+    w = GOLDEN_CASES["bf16_gated_k2"]
+    lw = make_weights(w)
+    layer = make_layer(w, lw)
+    try:
+        xs = [make_tokens(w.scaled(seed=w.seed + i)).pin_memory() for i in range(5)]
+        outs = [torch.zeros_like(x).pin_memory() for x in xs]
+        for x, o in zip(xs, outs):
+            layer.forward_host(x, o, wait=False)
+        layer.host_wait()
+        layer.check()
+        for x, o in zip(xs, outs):
+            ref, _ = oracle_layer(w, x=x, lw=lw)
+            assert max_rel_err(o, ref) <= 2e-2
+    finally:
+        layer.close()
+
+
 def test_argument_errors_are_reported_not_fatal():
     import flashmoe_b200 as flashmoe
     w = GOLDEN_CASES["bf16_gated_k2"]
