@@ -330,6 +330,10 @@ int fmoe_ctx_create(const fmoe_model_desc* model, const fmoe_ep_desc* ep, void* 
   }
   p.tiles_n0 = (I + g.tile_n0 - 1) / g.tile_n0;
   p.tiles_n1 = (H + g.tile_n1 - 1) / g.tile_n1;
+  if (static_cast<long long>(S) * k * p.tiles_n1 * 2 >= (1LL << 31)) {
+    free_ctx(c);
+    return set_error(FMOE_ERR_UNSUPPORTED, "tokens_per_rank * top_k * ceil(H / 256) is too large for the 32-bit arrival counters");
+  }
   p.landing_rows = g.landing_rows; p.max_mtiles = max_mtiles;
   p.owner = reinterpret_cast<const int32_t*>(c->work + w_owner);
   p.lidx = reinterpret_cast<const int32_t*>(c->work + w_lidx);
