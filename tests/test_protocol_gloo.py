@@ -123,15 +123,21 @@ def test_two_rank_exchange_matches_single_rank_oracle(name):
 def _failing_peer(rank, world, port, q):
     import datetime
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
-    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=10))
-    cb.initialize()
-    if rank == 1:
-        os._exit(0)          # leaves before the handle exchange, with nothing in flight
+    stage = "set-up"
     try:
+        dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=10))
+        cb.initialize()
+        dist.barrier()       # both ranks are up: what follows is the exchange itself
+        stage = "exchange"
+        if rank == 1:
+            os._exit(0)      # leaves before the handle exchange, with nothing in flight
         cb.all_gather_bytes(b"x" * 64)
         q.put("no error")
     except Exception as exc:  # the survivor learns of it on the host, before any launch
-        q.put("error: " + type(exc).__name__)
+        if rank == 0:
+            q.put(("error: " if stage == "exchange" else "set-up failed: ") + type(exc).__name__)
+    q.close()
+    q.join_thread()          # the queue's feeder thread has written the message before the hard exit
     os._exit(0)
 
 
