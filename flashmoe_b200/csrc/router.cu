@@ -59,6 +59,7 @@ struct Vec8;  // loads 8 consecutive elements as fp32
 template <>
 struct Vec8<__nv_bfloat16> {
   static constexpr bool kExactProducts = true;
+  static constexpr bool kIsBf16 = true;
   __device__ __forceinline__ static void load(const void* p, float (&f)[8]) {
     const uint4 u = __ldg(reinterpret_cast<const uint4*>(p));
     const uint32_t w[4] = {u.x, u.y, u.z, u.w};
@@ -72,6 +73,7 @@ struct Vec8<__nv_bfloat16> {
 template <>
 struct Vec8<__half> {
   static constexpr bool kExactProducts = true;
+  static constexpr bool kIsBf16 = false;
   __device__ __forceinline__ static void load(const void* p, float (&f)[8]) {
     const uint4 u = __ldg(reinterpret_cast<const uint4*>(p));
     const uint32_t w[4] = {u.x, u.y, u.z, u.w};
@@ -86,11 +88,46 @@ struct Vec8<__half> {
 template <>
 struct Vec8<float> {
   static constexpr bool kExactProducts = false;
+  static constexpr bool kIsBf16 = false;
   __device__ __forceinline__ static void load(const void* p, float (&f)[8]) {
     const float4 a = __ldg(reinterpret_cast<const float4*>(p));
     const float4 b = __ldg(reinterpret_cast<const float4*>(p) + 1);
     f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w;
     f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
+  }
+};
+
+// 8 consecutive elements as loaded (16 or 32 bytes), converted to fp32 only when they are used, so
+// that a load issued several iterations ahead does not stall the warp where it is issued.
+template <typename T>
+struct Raw8 {
+  static constexpr int kPieces = static_cast<int>(sizeof(T)) * 8 / 16;
+  uint4 q[kPieces];
+  __device__ __forceinline__ void fetch(const T* p) {
+#pragma unroll
+    for (int i = 0; i < kPieces; ++i) q[i] = __ldg(reinterpret_cast<const uint4*>(p) + i);
+  }
+  __device__ __forceinline__ void unpack(float (&f)[8]) const {
+    if constexpr (sizeof(T) == 4) {
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        f[4 * i] = __uint_as_float(q[i].x); f[4 * i + 1] = __uint_as_float(q[i].y);
+        f[4 * i + 2] = __uint_as_float(q[i].z); f[4 * i + 3] = __uint_as_float(q[i].w);
+      }
+    } else {
+      const uint32_t w[4] = {q[0].x, q[0].y, q[0].z, q[0].w};
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        if constexpr (sizeof(T) == 2 && Vec8<T>::kIsBf16) {
+          f[2 * i] = __uint_as_float(w[i] << 16);
+          f[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+        } else {
+          const float2 v = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
+          f[2 * i] = v.x;
+          f[2 * i + 1] = v.y;
+        }
+      }
+    }
   }
 };
 
@@ -139,7 +176,7 @@ __device__ __forceinline__ void vec8_from_smem<float>(const float* p, float (&f)
 
 // One warp owns TT consecutive tokens; the CTA walks the experts in groups of EG and the H axis
 // in chunks of 256 elements (one 8-element vector per lane).  The EG x 256 chunk of the router
-// weight is staged in shared memory (cp.async, double buffered) and shared by all warps, so the
+// weight is staged in shared memory (cp.async, a ring of 2 or 4 chunks) and shared by all warps, so the
 // weight matrix crosses L2 once per CTA instead of once per warp.
 //
 // The CTA's warps form TG token groups x ES expert parts: warp (tg, part) accumulates, for its TT
@@ -166,9 +203,15 @@ router_topk_kernel(const RouterParams p) {
   const T* __restrict__ Wr = static_cast<const T*>(p.weights);
   float* rows = s_row + static_cast<size_t>(tg) * TT * E;
 
-  auto stage = [&](int eg, int it, int buf) {
+  // weight chunks in flight: with few experts a chunk's arithmetic is shorter than an L2 round trip
+  constexpr bool kDeep = EG <= 16;
+  constexpr int NSTG = kDeep ? 4 : 2;
+  // chunk `it` of expert group `eg` -> ring slot it % NSTG; always commits a group (an empty one
+  // past the end), so that "all but the newest NSTG - 1 groups have landed" means chunk it is in
+  auto stage = [&](int eg, int it) {
+    const int buf = it % NSTG;
     const int v = it * 32 + lane;
-    if (v < nvec) {
+    if (it < iters && v < nvec) {
 #pragma unroll
       for (int e = warp; e < EG; e += WARPS) {
         T* dst = wbuf + (static_cast<size_t>(buf) * EG + e) * kChunk + lane * 8;
@@ -189,37 +232,85 @@ router_topk_kernel(const RouterParams p) {
 #pragma unroll
       for (int e = 0; e < EP; ++e) acc[t][e] = 0.0f;
 
-    stage(eg, 0, 0);
-    for (int it = 0; it < iters; ++it) {
-      if (it + 1 < iters) { stage(eg, it + 1, (it + 1) & 1); cp_async_wait<1>(); } else { cp_async_wait<0>(); }
-      __syncthreads();
-      const int v = it * 32 + lane;
-      if (v < nvec) {
-        float xv[TT][8];
+    // One 8-element vector of each of the warp's TT tokens per iteration.  With few experts
+    // (EG <= 16) there is little arithmetic per loaded byte, so the token vectors of the next PF
+    // iterations are kept in flight in registers; the order of the additions into acc[][] is the
+    // same either way.
+    auto accumulate = [&](int it, const float (&xv)[TT][8]) {
+      const T* wb = wbuf + (static_cast<size_t>(it % NSTG) * EG + part * EP) * kChunk + lane * 8;
+#pragma unroll
+      for (int e = 0; e < EP; ++e) {
+        float wv[8];
+        vec8_from_smem<T>(wb + e * kChunk, wv);
 #pragma unroll
         for (int t = 0; t < TT; ++t) {
-          const int tok = min(t0 + t, p.S - 1);  // ragged last group: recompute the last token
-          Vec8<T>::load(X + static_cast<size_t>(tok) * H + v * 8, xv[t]);
-        }
-        const T* wb = wbuf + (static_cast<size_t>(it & 1) * EG + part * EP) * kChunk + lane * 8;
 #pragma unroll
-        for (int e = 0; e < EP; ++e) {
-          float wv[8];
-          vec8_from_smem<T>(wb + e * kChunk, wv);
-#pragma unroll
-          for (int t = 0; t < TT; ++t) {
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-              if constexpr (Vec8<T>::kExactProducts) {
-                acc[t][e] = __fmaf_rn(xv[t][j], wv[j], acc[t][e]);
-              } else {
-                acc[t][e] = __fadd_rn(acc[t][e], __fmul_rn(xv[t][j], wv[j]));
-              }
+          for (int j = 0; j < 8; ++j) {
+            if constexpr (Vec8<T>::kExactProducts) {
+              acc[t][e] = __fmaf_rn(xv[t][j], wv[j], acc[t][e]);
+            } else {
+              acc[t][e] = __fadd_rn(acc[t][e], __fmul_rn(xv[t][j], wv[j]));
             }
           }
         }
       }
-      __syncthreads();
+    };
+    // iterations of token vectors in flight: 8 (fp32: 4) vectors of 16 (32) bytes per lane
+    constexpr int PF = kDeep ? (sizeof(T) == 4 ? (TT >= 4 ? 1 : 4 / TT) : 8 / TT) : 0;
+    if constexpr (PF > 0) {
+      Raw8<T> xr[PF][TT];
+      auto fetch = [&](int it, Raw8<T> (&slot)[TT]) {
+        const int v = it * 32 + lane;
+        if (it < iters && v < nvec) {
+#pragma unroll
+          for (int t = 0; t < TT; ++t) {
+            const int tok = min(t0 + t, p.S - 1);  // ragged last group: recompute the last token
+            slot[t].fetch(X + static_cast<size_t>(tok) * H + v * 8);
+          }
+        }
+      };
+#pragma unroll
+      for (int j = 0; j < PF; ++j) fetch(j, xr[j]);
+#pragma unroll
+      for (int j = 0; j < NSTG - 1; ++j) stage(eg, j);
+      for (int it0 = 0; it0 < iters; it0 += PF) {
+#pragma unroll
+        for (int j = 0; j < PF; ++j) {
+          const int it = it0 + j;
+          if (it < iters) {   // the same for every thread of the CTA
+            stage(eg, it + NSTG - 1);   // into the slot that chunk it - 1 left behind the last barrier
+            cp_async_wait<NSTG - 1>();
+            __syncthreads();
+            if (it * 32 + lane < nvec) {
+              float xv[TT][8];
+#pragma unroll
+              for (int t = 0; t < TT; ++t) xr[j][t].unpack(xv[t]);
+              accumulate(it, xv);
+            }
+            fetch(it + PF, xr[j]);
+            __syncthreads();
+          }
+        }
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < NSTG - 1; ++j) stage(eg, j);
+      for (int it = 0; it < iters; ++it) {
+        stage(eg, it + NSTG - 1);
+        cp_async_wait<NSTG - 1>();
+        __syncthreads();
+        const int v = it * 32 + lane;
+        if (v < nvec) {
+          float xv[TT][8];
+#pragma unroll
+          for (int t = 0; t < TT; ++t) {
+            const int tok = min(t0 + t, p.S - 1);  // ragged last group: recompute the last token
+            Vec8<T>::load(X + static_cast<size_t>(tok) * H + v * 8, xv[t]);
+          }
+          accumulate(it, xv);
+        }
+        __syncthreads();
+      }
     }
 #pragma unroll
     for (int t = 0; t < TT; ++t) {
@@ -331,7 +422,7 @@ cudaError_t launch_topk_eg(const RouterParams& p, cudaStream_t stream) {
   const int ctas = (p.S + TG * TT - 1) / (TG * TT);
   auto go = [&](auto kern, int eg) -> cudaError_t {
     const size_t rows = (static_cast<size_t>(TG) * TT * p.E * sizeof(float) + 15) & ~size_t(15);
-    const size_t smem = rows + 2 * static_cast<size_t>(eg) * 256 * sizeof(T);
+    const size_t smem = rows + (eg <= 16 ? 4 : 2) * static_cast<size_t>(eg) * 256 * sizeof(T);
     if (smem > 48 * 1024) {
       cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                            static_cast<int>(smem));
@@ -346,8 +437,12 @@ cudaError_t launch_topk_eg(const RouterParams& p, cudaStream_t stream) {
   return go(router_topk_kernel<T, TT, 8, TG, ES>, 8);
 }
 
-// Tokens per CTA = TG * TT: the largest that still gives about one CTA per SM.  With many
-// experts the experts of a group are split over ES = 4 warps per token group.
+// A CTA holds TG = 4 token groups x ES expert parts of warps, each warp TT tokens.  With many
+// experts: ES = 4, and TT the largest that still fills the SMs with warps.  With few experts a
+// warp has little arithmetic per token and the kernel lives on how many warps hide its latencies:
+// two tokens per warp and the experts split over two warps measured fastest from 1 K to 8 K tokens
+// (Scout shapes, 1024 tokens: 21.5 us for both router kernels, against 24-43 us for the other
+// splits).
 template <typename T>
 cudaError_t launch_topk(const RouterParams& p, cudaStream_t stream) {
   if (p.E >= 64) {
@@ -355,10 +450,7 @@ cudaError_t launch_topk(const RouterParams& p, cudaStream_t stream) {
     if (p.S >= 120 * 8) return launch_topk_eg<T, 2, 4, 4>(p, stream);
     return launch_topk_eg<T, 1, 4, 4>(p, stream);
   }
-  if (p.S >= 120 * 32) return launch_topk_eg<T, 4, 8, 1>(p, stream);
-  if (p.S >= 120 * 16) return launch_topk_eg<T, 4, 4, 1>(p, stream);
-  if (p.S >= 120 * 8) return launch_topk_eg<T, 2, 4, 1>(p, stream);
-  return launch_topk_eg<T, 1, 4, 1>(p, stream);
+  return launch_topk_eg<T, 2, 4, 2>(p, stream);
 }
 
 }  // namespace
