@@ -12,12 +12,12 @@ from __future__ import annotations
 import ctypes as C
 
 from . import _native as N
-from . import cb, router
+from . import cb, reference, router
 from .cb import get_local_rank
 from .jit import (ActivationType, ContextHandle, DataType, ForwardArgs, InitArgs, MLPType,
                   Topology, _get_compiled)
 
-__all__ = ["initialize", "forward", "finalize", "router", "cb", "get_local_rank", "InitArgs",
+__all__ = ["initialize", "forward", "finalize", "get_workspace_bytes", "router", "reference", "cb", "get_local_rank", "InitArgs",
            "ForwardArgs", "ContextHandle", "Topology", "MLPType", "ActivationType", "DataType",
            "FlashMoEError"]
 FlashMoEError = N.FlashMoEError
@@ -134,6 +134,20 @@ def initialize(arg: InitArgs) -> ContextHandle:
                          expert_map=arg.expert_map, rank_map=arg.rank_map, stream_ptr=arg.stream_ptr)
     cb.sync_all(arg.stream_ptr)
     return ContextHandle(mod, ctx)
+
+
+def get_workspace_bytes(arg: InitArgs, ep_world: int = None, num_local_experts: int = None) -> dict:
+    """What `initialize(arg)` would allocate on this rank, without allocating or touching a GPU
+    (the reference's flashmoe::getWorkspaceBytes, bootstrap.cuh:377-410, is C++ only):
+    {"symmetric": bytes of the block every peer maps, "workspace": bytes of the private part}."""
+    world = ep_world if ep_world is not None else (arg.ep_world or 1)
+    nlx = num_local_experts if num_local_experts is not None else (arg.num_local_experts or arg.num_experts // world)
+    ep = N.EpDesc(world, 0, 0, 0, nlx, int(Topology.NVLINK_ONLY), None, None)
+    desc = _model_desc(arg)
+    symm, work = C.c_int64(), C.c_int64()
+    N.check(N.lib().fmoe_workspace_bytes(C.byref(desc), C.byref(ep), C.byref(symm), C.byref(work)),
+            "get_workspace_bytes")
+    return {"symmetric": symm.value, "workspace": work.value}
 
 
 def forward(handle: ContextHandle, args: ForwardArgs) -> None:

@@ -90,7 +90,14 @@ struct fmoe_ctx {
   size_t work_bytes = 0;
   MoeParams params{};                   // everything but the per-forward pointers
   CUtensorMap maps[5];
-  const void* map_src[3] = {nullptr, nullptr, nullptr};  // up, up_v, down the maps were built for
+  // TMA descriptors of the weight sets seen so far (one per layer served by this context),
+  // oldest replaced first once FMOE_LAYER_CACHE are held
+  struct WeightMaps {
+    const void* src[3] = {nullptr, nullptr, nullptr};  // up, up_v, down
+    CUtensorMap m[3];
+  };
+  std::vector<WeightMaps> layer_maps;
+  size_t layer_next = 0;
   void* stage_tokens = nullptr;         // host-buffer entry point staging
   void* stage_out = nullptr;
   // pipelined host-buffer entry point: two slots, a copy-in and a copy-out stream, events per slot
@@ -151,6 +158,76 @@ int validate_model(const fmoe_model_desc* m) {
 
 namespace {
 
+// Sizes and offsets of everything a context allocates, from the layer's description alone (no
+// device call): the symmetric block (mapped by every peer) and the private workspace.
+struct Plan {
+  int round_ec = 0, landing_rows = 0, max_mtiles = 0;
+  SymmLayout lay{};
+  size_t w_y = 0, w_done = 0, w_ctl = 0, w_status = 0, w_trace = 0, w_table = 0, w_routes = 0, w_owner = 0,
+         w_lidx = 0, w_local = 0, work_bytes = 0;
+  size_t weight_plane_bytes = 0;   // fp32 layers: the BF16 planes of up, up_v and down
+};
+
+Plan plan_sizes(const fmoe_model_desc& m, int W, int nLx) {
+  Plan pl;
+  const int S = m.tokens_per_rank, H = m.token_dim, I = m.ffn_size, k = m.top_k, E = m.num_experts;
+  const int EC = m.expert_peer_capacity;
+  const int eb = m.data_type == FMOE_DT_FP32 ? 4 : 2, planes = m.data_type == FMOE_DT_FP32 ? 3 : 1;
+  pl.round_ec = static_cast<int>(align_up(EC, kTileM));
+  const long long cap_a = static_cast<long long>(nLx) * align_up(static_cast<size_t>(W) * EC, kTileM);
+  const long long cap_b = static_cast<long long>(align_up(static_cast<size_t>(W) * S * k, kTileM)) +
+                          static_cast<long long>(nLx) * kTileM;
+  pl.landing_rows = static_cast<int>(cap_a < cap_b ? cap_a : cap_b);
+  pl.max_mtiles = pl.landing_rows / kTileM;
+  // symmetric block layout (same arithmetic on every rank)
+  SymmLayout& L = pl.lay;
+  size_t off = 0;
+  L.cnt_table = off; off = align_up(off + sizeof(int32_t) * 2 * W * E, 256);
+  L.cnt_flag = off; off = align_up(off + sizeof(uint64_t) * 2 * W, 256);
+  L.disp_arrived = off; off = align_up(off + sizeof(uint32_t) * W * nLx, 256);
+  L.ret_arrived = off; off = align_up(off + sizeof(uint32_t), 256);
+  L.landing_meta = off; off = align_up(off + sizeof(uint32_t) * pl.landing_rows, 1024);
+  L.landing = off; off = align_up(off + static_cast<size_t>(planes) * pl.landing_rows * H * 2, 1024);
+  L.ret = off; off = align_up(off + static_cast<size_t>(S) * k * H * eb, 1024);
+  L.total = off;
+  // private workspace
+  size_t w = 0;
+  pl.w_y = w; w = align_up(w + static_cast<size_t>(planes) * pl.landing_rows * I * 2, 1024);
+  pl.w_done = w; w = align_up(w + sizeof(uint32_t) * pl.max_mtiles, 256);
+  pl.w_ctl = w; w = align_up(w + 256, 256);   // ticket, done_ctas, abort, epoch
+  pl.w_status = w; w = align_up(w + sizeof(fmoe_status), 256);
+  pl.w_trace = w; w = align_up(w + sizeof(unsigned long long) * 8 * 256, 256);
+  pl.w_table = w; w = align_up(w + sizeof(TokenSlot) * E * pl.round_ec, 256);
+  pl.w_routes = w; w = align_up(w + sizeof(Route) * S * k, 256);
+  pl.w_owner = w; w = align_up(w + sizeof(int32_t) * E, 256);
+  pl.w_lidx = w; w = align_up(w + sizeof(int32_t) * E, 256);
+  pl.w_local = w; w = align_up(w + sizeof(int32_t) * W * nLx, 256);
+  pl.work_bytes = w;
+  if (planes == 3)
+    pl.weight_plane_bytes = static_cast<size_t>(nLx) * I * H * 2 * 3 * (m.mlp_type == FMOE_MLP_GATED ? 3 : 2);
+  return pl;
+}
+
+// The argument checks of fmoe_ctx_create that need no device.
+int check_layer(const fmoe_model_desc* model, const fmoe_ep_desc* ep) {
+  int rc = validate_model(model);
+  if (rc != FMOE_OK) return rc;
+  if (ep == nullptr) return set_error(FMOE_ERR_INVALID_ARG, "ep description is null");
+  if (model->data_type == FMOE_DT_FP64)
+    return set_error(FMOE_ERR_UNSUPPORTED, "the expert kernels handle BF16, FP16 and FP32; FP64 is not built");
+  if (ep->topology != FMOE_TOPO_NVLINK_ONLY)
+    return set_error(FMOE_ERR_UNSUPPORTED, "only Topology.NVLINK_ONLY (one NVLink box) is implemented");
+  const int W = ep->ep_world, E = model->num_experts;
+  if (W < 1 || W > FMOE_MAX_WORLD)
+    return set_error(FMOE_ERR_UNSUPPORTED, "ep_world must be between 1 and " + std::to_string(FMOE_MAX_WORLD));
+  if (ep->ep_rank < 0 || ep->ep_rank >= W) return set_error(FMOE_ERR_INVALID_ARG, "ep_rank out of range");
+  if (ep->num_local_experts < 1 || ep->num_local_experts * W != E)
+    return set_error(FMOE_ERR_INVALID_ARG, "every rank must hold num_experts / ep_world experts");
+  if (static_cast<long long>(W) * E > 4096)
+    return set_error(FMOE_ERR_UNSUPPORTED, "ep_world * num_experts must not exceed 4096");
+  return FMOE_OK;
+}
+
 void free_ctx(fmoe_ctx* c) {
   if (c == nullptr) return;
   for (int r = 0; r < FMOE_MAX_WORLD; ++r)
@@ -192,27 +269,25 @@ const char* fmoe_last_error(void) { return t_error.c_str(); }
 
 uint64_t fmoe_launch_count(void) { return g_launches; }
 
+int fmoe_workspace_bytes(const fmoe_model_desc* model, const fmoe_ep_desc* ep, int64_t* symm_bytes_out,
+                         int64_t* workspace_bytes_out) {
+  const int rc = check_layer(model, ep);
+  if (rc != FMOE_OK) return rc;
+  const Plan pl = plan_sizes(*model, ep->ep_world, ep->num_local_experts);
+  if (symm_bytes_out) *symm_bytes_out = static_cast<int64_t>(pl.lay.total);
+  if (workspace_bytes_out) *workspace_bytes_out = static_cast<int64_t>(pl.work_bytes + pl.weight_plane_bytes);
+  return FMOE_OK;
+}
+
 int fmoe_ctx_create(const fmoe_model_desc* model, const fmoe_ep_desc* ep, void* stream, fmoe_ctx** out) {
   if (out == nullptr) return set_error(FMOE_ERR_INVALID_ARG, "out is null");
   *out = nullptr;
-  int rc = validate_model(model);
+  int rc = check_layer(model, ep);
   if (rc != FMOE_OK) return rc;
-  if (ep == nullptr) return set_error(FMOE_ERR_INVALID_ARG, "ep description is null");
-  if (model->data_type == FMOE_DT_FP64)
-    return set_error(FMOE_ERR_UNSUPPORTED, "the expert kernels handle BF16, FP16 and FP32; FP64 is not built");
-  if (ep->topology != FMOE_TOPO_NVLINK_ONLY)
-    return set_error(FMOE_ERR_UNSUPPORTED, "only Topology.NVLINK_ONLY (one NVLink box) is implemented");
-  const int W = ep->ep_world, E = model->num_experts;
-  if (W < 1 || W > FMOE_MAX_WORLD)
-    return set_error(FMOE_ERR_UNSUPPORTED, "ep_world must be between 1 and " + std::to_string(FMOE_MAX_WORLD));
-  if (ep->ep_rank < 0 || ep->ep_rank >= W) return set_error(FMOE_ERR_INVALID_ARG, "ep_rank out of range");
   if (ep->expert_map == nullptr || ep->rank_map == nullptr)
     return set_error(FMOE_ERR_INVALID_ARG, "expert_map and rank_map are required");
-  if (ep->num_local_experts < 1 || ep->num_local_experts * W != E)
-    return set_error(FMOE_ERR_INVALID_ARG, "every rank must hold num_experts / ep_world experts");
+  const int W = ep->ep_world, E = model->num_experts;
   const int nLx = ep->num_local_experts;
-  if (static_cast<long long>(W) * E > 4096)
-    return set_error(FMOE_ERR_UNSUPPORTED, "ep_world * num_experts must not exceed 4096");
 
   fmoe_ctx* c = new (std::nothrow) fmoe_ctx();
   if (c == nullptr) return set_error(FMOE_ERR_NO_MEMORY, "host allocation failed");
@@ -248,26 +323,16 @@ int fmoe_ctx_create(const fmoe_model_desc* model, const fmoe_ep_desc* ep, void* 
   fmoe_geometry& g = c->geo;
   g.tile_m = kTileM; g.tile_k = kTileK;
   g.tile_n0 = gated ? 128 : 256; g.tile_n1 = 256;
-  g.round_ec = static_cast<int>(align_up(EC, kTileM));
-  const long long cap_a = static_cast<long long>(nLx) * align_up(static_cast<size_t>(W) * EC, kTileM);
-  const long long cap_b = static_cast<long long>(align_up(static_cast<size_t>(W) * S * k, kTileM)) +
-                          static_cast<long long>(nLx) * kTileM;
-  g.landing_rows = static_cast<int>(cap_a < cap_b ? cap_a : cap_b);
+  const Plan pl = plan_sizes(*model, W, nLx);
+  g.round_ec = pl.round_ec;
+  g.landing_rows = pl.landing_rows;
   g.grid = sms & ~1; g.threads = kThreads;   // CTA pairs: an even number of CTAs, one per SM
   g.smem_bytes = static_cast<int>(moe_smem_bytes(W, E, nLx));
   if (g.smem_bytes > 227 * 1024) { free_ctx(c); return set_error(FMOE_ERR_UNSUPPORTED, "tables do not fit in shared memory"); }
 
   // symmetric block layout (same arithmetic on every rank)
   SymmLayout& L = c->lay;
-  size_t off = 0;
-  L.cnt_table = off; off = align_up(off + sizeof(int32_t) * 2 * W * E, 256);
-  L.cnt_flag = off; off = align_up(off + sizeof(uint64_t) * 2 * W, 256);
-  L.disp_arrived = off; off = align_up(off + sizeof(uint32_t) * W * nLx, 256);
-  L.ret_arrived = off; off = align_up(off + sizeof(uint32_t), 256);
-  L.landing_meta = off; off = align_up(off + sizeof(uint32_t) * g.landing_rows, 1024);
-  L.landing = off; off = align_up(off + static_cast<size_t>(c->planes) * g.landing_rows * H * 2, 1024);
-  L.ret = off; off = align_up(off + static_cast<size_t>(S) * k * H * c->eb, 1024);
-  L.total = off;
+  L = pl.lay;
   g.symm_bytes = static_cast<int64_t>(L.total);
 
   ce = cudaMalloc(&c->symm, L.total);
@@ -279,18 +344,10 @@ int fmoe_ctx_create(const fmoe_model_desc* model, const fmoe_ep_desc* ep, void* 
   c->peers[c->rank] = c->symm;
 
   // private workspace
-  const int max_mtiles = g.landing_rows / kTileM;
-  size_t w = 0;
-  const size_t w_y = w; w = align_up(w + static_cast<size_t>(c->planes) * g.landing_rows * I * 2, 1024);
-  const size_t w_done = w; w = align_up(w + sizeof(uint32_t) * max_mtiles, 256);
-  const size_t w_ctl = w; w = align_up(w + 256, 256);   // ticket, done_ctas, abort, epoch
-  const size_t w_status = w; w = align_up(w + sizeof(fmoe_status), 256);
-  const size_t w_trace = w; w = align_up(w + sizeof(unsigned long long) * 8 * 256, 256);
-  const size_t w_table = w; w = align_up(w + sizeof(TokenSlot) * E * g.round_ec, 256);
-  const size_t w_routes = w; w = align_up(w + sizeof(Route) * S * k, 256);
-  const size_t w_owner = w; w = align_up(w + sizeof(int32_t) * E, 256);
-  const size_t w_lidx = w; w = align_up(w + sizeof(int32_t) * E, 256);
-  const size_t w_local = w; w = align_up(w + sizeof(int32_t) * W * nLx, 256);
+  const int max_mtiles = pl.max_mtiles;
+  const size_t w_y = pl.w_y, w_done = pl.w_done, w_ctl = pl.w_ctl, w_status = pl.w_status, w_trace = pl.w_trace,
+               w_table = pl.w_table, w_routes = pl.w_routes, w_owner = pl.w_owner, w_lidx = pl.w_lidx,
+               w_local = pl.w_local, w = pl.work_bytes;
   c->work_bytes = w;
   g.workspace_bytes = static_cast<int64_t>(w);
   ce = cudaMalloc(&c->work, w);
@@ -482,12 +539,27 @@ int fmoe_forward(fmoe_ctx* ctx, const fmoe_forward_args* a, void* stream) {
     if (gated)
       FMOE_CUDA(launch_split_planes(static_cast<const float*>(a->local_expert_up_v), ctx->wsplit + ctx->wsplit_up_v, n, st));
     FMOE_CUDA(launch_split_planes(static_cast<const float*>(a->local_expert_down), ctx->wsplit + ctx->wsplit_down, n, st));
-  } else if (ctx->map_src[0] != a->local_expert_up || ctx->map_src[1] != up_v || ctx->map_src[2] != a->local_expert_down) {
-    int rc = make_map(&ctx->maps[2], p.ab_format, a->local_expert_up, static_cast<uint64_t>(p.nLx) * p.I, p.H);
-    if (rc == FMOE_OK) rc = make_map(&ctx->maps[3], p.ab_format, up_v, static_cast<uint64_t>(p.nLx) * p.I, p.H);
-    if (rc == FMOE_OK) rc = make_map(&ctx->maps[4], p.ab_format, a->local_expert_down, static_cast<uint64_t>(p.nLx) * p.H, p.I);
-    if (rc != FMOE_OK) return rc;
-    ctx->map_src[0] = a->local_expert_up; ctx->map_src[1] = up_v; ctx->map_src[2] = a->local_expert_down;
+  } else {
+    const fmoe_ctx::WeightMaps* hit = nullptr;
+    for (const auto& wm : ctx->layer_maps)
+      if (wm.src[0] == a->local_expert_up && wm.src[1] == up_v && wm.src[2] == a->local_expert_down) { hit = &wm; break; }
+    if (hit == nullptr) {
+      fmoe_ctx::WeightMaps wm;
+      int rc = make_map(&wm.m[0], p.ab_format, a->local_expert_up, static_cast<uint64_t>(p.nLx) * p.I, p.H);
+      if (rc == FMOE_OK) rc = make_map(&wm.m[1], p.ab_format, up_v, static_cast<uint64_t>(p.nLx) * p.I, p.H);
+      if (rc == FMOE_OK) rc = make_map(&wm.m[2], p.ab_format, a->local_expert_down, static_cast<uint64_t>(p.nLx) * p.H, p.I);
+      if (rc != FMOE_OK) return rc;
+      wm.src[0] = a->local_expert_up; wm.src[1] = up_v; wm.src[2] = a->local_expert_down;
+      if (ctx->layer_maps.size() < FMOE_LAYER_CACHE) {
+        ctx->layer_maps.push_back(wm);
+        hit = &ctx->layer_maps.back();
+      } else {
+        ctx->layer_maps[ctx->layer_next] = wm;
+        hit = &ctx->layer_maps[ctx->layer_next];
+        ctx->layer_next = (ctx->layer_next + 1) % FMOE_LAYER_CACHE;
+      }
+    }
+    ctx->maps[2] = hit->m[0]; ctx->maps[3] = hit->m[1]; ctx->maps[4] = hit->m[2];
   }
   p.tokens = a->tokens; p.expert_counts = a->expert_counts;
   p.bias_up = a->local_bias_up; p.bias_up_v = a->local_bias_up_v; p.bias_down = a->local_bias_down;

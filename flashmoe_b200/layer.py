@@ -65,6 +65,37 @@ class MoELayer:
             logit_bias=ptr(self.logit_bias))
         torch.cuda.synchronize(self.dev)
 
+        self._layers = [dict(router_w=self.router_w, up=self.up, up_v=self.up_v, down=self.down,
+                             b_up=self.b_up, b_up_v=self.b_up_v, b_down=self.b_down,
+                             logit_bias=self.logit_bias)]
+        self._take = take
+
+    # several layers of one model through ONE context: a forward only reads the weights it is
+    # handed, and the context keeps the TMA descriptors of every weight set it has seen
+    def add_layer(self, weights: LayerWeights) -> int:
+        """Device copies of another layer's weights (same shapes); returns its index."""
+        take = self._take
+        nz = lambda t: t is not None and bool((t != 0).any())
+        self._layers.append(dict(
+            router_w=weights.router.to(self.dev), up=take(weights.up), up_v=take(weights.up_v),
+            down=take(weights.down), b_up=take(weights.bias_up) if nz(weights.bias_up) else None,
+            b_up_v=take(weights.bias_up_v) if nz(weights.bias_up_v) else None,
+            b_down=take(weights.bias_down) if nz(weights.bias_down) else None,
+            logit_bias=None if weights.logit_bias is None else weights.logit_bias.to(self.dev)))
+        torch.cuda.synchronize(self.dev)
+        return len(self._layers) - 1
+
+    def select_layer(self, index: int) -> None:
+        """The next `route` / `experts` / `forward` calls use layer `index`'s weights."""
+        L = self._layers[index]
+        ptr = lambda t: 0 if t is None else t.data_ptr()
+        f, r = self.fargs, self.rargs
+        f.local_expert_up, f.local_expert_down = L["up"].data_ptr(), L["down"].data_ptr()
+        f.local_bias_up, f.local_bias_down = ptr(L["b_up"]), ptr(L["b_down"])
+        if L["up_v"] is not None:
+            f.local_expert_up_v, f.local_bias_up_v = L["up_v"].data_ptr(), ptr(L["b_up_v"])
+        r.weights, r.logit_bias = L["router_w"].data_ptr(), ptr(L["logit_bias"])
+
     # the three calls of the hot path, on self.stream
     def route(self) -> None:
         flashmoe.router.forward(self.router_handle, self.handle, self.rargs)

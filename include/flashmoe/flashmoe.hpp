@@ -126,6 +126,17 @@ inline Context initialize(const MoEArgs& args, const LayerDesc& layer, int arch,
   if (args.epWorld == 1) check(fmoe_ctx_commit(c.handle), "flashmoe::initialize");
   return c;
 }
+// flashmoe::getWorkspaceBytes (bootstrap.cuh:377-410): device bytes initialize would allocate on
+// this rank (symmetric block + private workspace), computed on the host.
+inline size_t getWorkspaceBytes(const MoEArgs& args, const LayerDesc& layer = LayerDesc{}, int arch = 1000) {
+  const fmoe_model_desc m = modelDesc(args, layer, arch);
+  fmoe_ep_desc ep{};
+  ep.ep_world = args.epWorld; ep.ep_rank = args.epRank; ep.my_pe = args.myPE; ep.device_id = layer.deviceId;
+  ep.num_local_experts = args.numLocalExperts; ep.topology = static_cast<int32_t>(args.topo);
+  int64_t symm = 0, work = 0;
+  check(fmoe_workspace_bytes(&m, &ep, &symm, &work), "flashmoe::getWorkspaceBytes");
+  return static_cast<size_t>(symm + work);
+}
 // Peer mapping for epWorld > 1 (replaces nvshmem_malloc / nvshmem_ptr, bootstrap.cuh:141-151).
 inline std::vector<unsigned char> exportSymmetric(Context& c) {
   std::vector<unsigned char> h(FMOE_IPC_HANDLE_BYTES);

@@ -117,6 +117,14 @@ enum {
 int fmoe_ctx_create(const fmoe_model_desc* model, const fmoe_ep_desc* ep, void* stream,
                     fmoe_ctx** out);
 
+/* Replaces flashmoe::getWorkspaceBytes (bootstrap.cuh:377-410): what fmoe_ctx_create would
+ * allocate for this description on this rank, without allocating or touching a device:
+ * the symmetric block and the private workspace (for FP32 layers including the BF16 planes of
+ * the expert weights).  Same argument checks as fmoe_ctx_create; expert_map / rank_map may be
+ * null.  Either output may be null. */
+int fmoe_workspace_bytes(const fmoe_model_desc* model, const fmoe_ep_desc* ep,
+                         int64_t* symm_bytes_out, int64_t* workspace_bytes_out);
+
 /* Replaces nvshmem_malloc + nvshmem_ptr (bootstrap.cuh:141-151, 239-249): the symmetric
  * block is an ordinary device allocation shared through CUDA IPC.  Export this rank's
  * handle, gather the handles by any host-side means, import every peer's, then commit.
@@ -140,7 +148,13 @@ int fmoe_ctx_destroy(fmoe_ctx* ctx, void* stream);
 
 /* Replaces moe::forwardHost / moe_forward (moe.cuh:255-260; flashmoe/bindings.py:112-140):
  * one launch of the persistent kernel (dispatch, expert GEMMs, combine) on `stream`.
- * Every rank of the group must call it the same number of times. */
+ * Every rank of the group must call it the same number of times.
+ * One context serves every layer of a model that shares this description: forwards on a
+ * stream are ordered, the epoch protocol needs nothing cleared between them, and the TMA
+ * descriptors of up to FMOE_LAYER_CACHE distinct (up, up_v, down) weight sets are kept, so
+ * alternating between layers costs no descriptor encoding (the reference builds one Context
+ * per layer, each with its own symmetric heap). */
+#define FMOE_LAYER_CACHE 128
 int fmoe_forward(fmoe_ctx* ctx, const fmoe_forward_args* args, void* stream);
 
 /* Replaces initializeGate / gate_initialize (bootstrap.cuh:413-447; bindings.py:238-264). */

@@ -41,6 +41,19 @@ int main() {
     MoEArgs a(2, 128, 256, 256, 128, 128, 128, 128, 64, 64, 128, 148, 0, 0, 1, 0, 8, 8, Topology::MIXED);
     expect_throw("topology", "NVLINK_ONLY", [&] { initialize(a, layer, 1000, emap, rmap, nullptr); });
   }
+  {
+    // getWorkspaceBytes needs no device: 128 tokens, H = I = 256, 8 experts on one rank, k = 2, BF16.
+    // It must at least hold the landing rows, the GEMM0 output and the return rows.
+    MoEArgs a(2, 128, 256, 256, 128, 128, 128, 128, 64, 64, 128, 148, 0, 0, 1, 0, 8, 8, Topology::NVLINK_ONLY);
+    const size_t bytes = getWorkspaceBytes(a, layer);
+    const size_t floor = static_cast<size_t>(128) * 2 * 256 * 2 * 3;
+    if (bytes < floor || bytes > 64u * 1024 * 1024) {
+      std::printf("FAIL getWorkspaceBytes: %zu\n", bytes);
+      ++fails;
+    }
+    MoEArgs bad(2, 128, 100, 256, 128, 128, 128, 128, 64, 64, 128, 148, 0, 0, 1, 0, 8, 8, Topology::NVLINK_ONLY);
+    expect_throw("getWorkspaceBytes tokenDim", "token dimension", [&] { getWorkspaceBytes(bad, layer); });
+  }
   static_assert(sizeof(TPS) == 8, "routing-table entry is 8 bytes");
   std::printf(fails == 0 ? "FACADE_OK\n" : "FACADE_FAILED\n");
   return fails;

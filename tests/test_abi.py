@@ -73,6 +73,30 @@ def test_bad_expert_maps_are_rejected():
     assert rc == 1
 
 
+def test_workspace_bytes_follow_the_description_without_a_device():
+    """fmoe_workspace_bytes / flashmoe.get_workspace_bytes (the reference's getWorkspaceBytes): host
+    arithmetic only.  Scout shapes on 8 ranks, no drop: the landing area holds every rank's 1024
+    rows plus one tile of slack per local expert, the return area this rank's 1024 rows."""
+    S, H, I, E, W = 1024, 5120, 8192, 16, 8
+    arg = flashmoe.InitArgs(flashmoe.DataType.BF16, S, H, I, E, 1, 1000, flashmoe.MLPType.GATED,
+                            flashmoe.ActivationType.SILU, 0, 0, expert_peer_capacity=S)
+    b = flashmoe.get_workspace_bytes(arg, ep_world=W)
+    rows = W * S + (E // W) * 128
+    assert rows * H * 2 + S * H * 2 <= b["symmetric"] <= rows * H * 2 + S * H * 2 + (1 << 20)
+    assert rows * I * 2 <= b["workspace"] <= rows * I * 2 + (4 << 20)
+    one = flashmoe.get_workspace_bytes(arg, ep_world=1)
+    assert one["symmetric"] < b["symmetric"]
+    # FP32 layers add the three BF16 planes of the local experts' weights
+    arg32 = flashmoe.InitArgs(flashmoe.DataType.FP32, 128, 1024, 2048, 8, 2, 1000, flashmoe.MLPType.GATED,
+                              flashmoe.ActivationType.SILU, 0, 0, expert_peer_capacity=128)
+    assert flashmoe.get_workspace_bytes(arg32)["workspace"] >= 8 * 1024 * 2048 * 2 * 3 * 3
+    # the same checks as create
+    desc, ep = _desc(token_dim=100), N.EpDesc(1, 0, 0, 0, 8, 0, None, None)
+    out = C.c_int64()
+    assert N.lib().fmoe_workspace_bytes(C.byref(desc), C.byref(ep), C.byref(out), None) == 1
+    assert "token dimension" in N.lib().fmoe_last_error().decode()
+
+
 def test_python_api_surface_matches_the_reference():
     a = flashmoe.InitArgs(flashmoe.DataType.BF16, 1024, 5120, 8192, 16, 1, 1000, flashmoe.MLPType.GATED,
                           flashmoe.ActivationType.SILU, 0, 0)
@@ -92,6 +116,11 @@ def test_python_api_surface_matches_the_reference():
         assert hasattr(flashmoe, name)
     for name in ("initialize", "forward", "finalize", "RouterForwardArgs"):
         assert hasattr(flashmoe.router, name)
+    for name in ("initialize", "forward", "RefForwardArgs"):
+        assert hasattr(flashmoe.reference, name)
+    r = flashmoe.reference.RefForwardArgs(1, 2, 3, 4, 5, 6, 7, 8, expert_up_v=9, bias_up_v=10)
+    assert (r.expert_up, r.expert_down, r.bias_up, r.bias_down, r.ref_input, r.ref_interim0, r.ref_interim1,
+            r.ref_out, r.expert_up_v, r.bias_up_v) == (1, 2, 3, 4, 5, 6, 7, 8, 9, 10)
 
 
 def test_initialize_without_a_gpu_fails_loudly():
@@ -102,3 +131,5 @@ def test_initialize_without_a_gpu_fails_loudly():
                           flashmoe.ActivationType.SILU, 0, 0)
     with pytest.raises(flashmoe.FlashMoEError):
         flashmoe.initialize(a)
+    with pytest.raises(RuntimeError):          # the checker has no CPU path either
+        flashmoe.reference.initialize(a)

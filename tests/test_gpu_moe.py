@@ -89,6 +89,39 @@ def test_half_width_gemm1_tickets(mode, monkeypatch):
         layer.close()
 
 
+def test_one_context_serves_several_layers():
+    """Three layers of one model (same shapes, different weights) run through ONE context, in turn
+    and repeatedly: every forward equals what a context of its own gives for that layer, bit for
+    bit, and after the first visit a layer's forward builds no new TMA descriptors (the same
+    number of launches, nothing allocated).  Sizes match the host-side query."""
+    import flashmoe_b200 as flashmoe
+    w = GOLDEN_CASES["bf16_gated_k2"]
+    sets = [make_weights(w.scaled(seed=w.seed + 100 * i)) for i in range(3)]
+    x = make_tokens(w)
+    own = []
+    for lw in sets:
+        layer = make_layer(w, lw)
+        try:
+            own.append(layer.forward(x).cpu())
+            ref, _ = oracle_layer(w, x=x, lw=lw)
+            assert max_rel_err(own[-1], ref) <= REL_TOL[int(w.data_type)]
+        finally:
+            layer.close()
+    assert not torch.equal(own[0], own[1])
+    shared = make_layer(w, sets[0])
+    try:
+        g = shared.geometry()
+        q = flashmoe.get_workspace_bytes(shared.args)
+        assert q == {"symmetric": g.symm_bytes, "workspace": g.workspace_bytes}
+        idx = [0, shared.add_layer(sets[1]), shared.add_layer(sets[2])]
+        for _ in range(3):
+            for i in (0, 1, 2, 1, 0):
+                shared.select_layer(idx[i])
+                assert torch.equal(shared.forward(x).cpu(), own[i]), i
+    finally:
+        shared.close()
+
+
 def test_forwards_replay_from_a_cuda_graph():
     """The reference times its kernel by capturing many forwards in one CUDA graph and replaying
     it (quickstart.py:264-291).  Nothing on the host changes between launches here either: the

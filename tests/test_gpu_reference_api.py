@@ -1,0 +1,82 @@
+"""`flashmoe.reference`, the unfused on-GPU checker a caller runs beside the fused forward
+(the reference's quickstart.py:137-160): the same call sequence, the reference's own acceptance
+measure, and every element of the benchmark shapes compared at full size."""
+import pytest
+import torch
+
+import flashmoe_b200 as flashmoe
+from cases import GOLDEN_CASES
+from helpers import REL_TOL, max_rel_err, oracle_layer
+from flashmoe_b200.workloads import CONFIGS, TORCH_DTYPE, make_tokens, make_weights
+
+pytestmark = pytest.mark.gpu
+
+
+def reference_out(layer):
+    """The quickstart's checker call for a world-1 `MoELayer` whose router + forward just ran."""
+    w = layer.w
+    S, H, I = w.tokens_per_rank, w.token_dim, w.ffn_size
+    dt, dev = TORCH_DTYPE[w.data_type], layer.dev
+    ptr = lambda t: 0 if t is None else t.data_ptr()
+    rows = max(S, -(-w.expert_peer_capacity // 128) * 128)
+    bufs = [torch.empty(rows, n, dtype=dt, device=dev) for n in (H, I, H)]
+    ref_out = torch.full((S, H), 7.0, dtype=dt, device=dev)      # the checker zeroes it itself
+    rea = flashmoe.reference.RefForwardArgs(
+        expert_up=layer.up.data_ptr(), expert_down=layer.down.data_ptr(), bias_up=ptr(layer.b_up),
+        bias_down=ptr(layer.b_down), ref_input=bufs[0].data_ptr(), ref_interim0=bufs[1].data_ptr(),
+        ref_interim1=bufs[2].data_ptr(), ref_out=ref_out.data_ptr(), expert_up_v=ptr(layer.up_v),
+        bias_up_v=ptr(layer.b_up_v))
+    handle = flashmoe.reference.initialize(layer.args)
+    torch.cuda.synchronize(dev)
+    flashmoe.reference.forward(handle, layer.handle.mod.get_tIdx(layer.handle.context), layer.fargs, rea)
+    layer.stream.synchronize()
+    return ref_out
+
+
+def mismatch_fraction(out, ref):
+    """The reference's acceptance measure (quickstart.py:158-160)."""
+    ok = torch.isclose(out.float(), ref.float(), rtol=8e-2, atol=8e-3).sum().item()
+    return 1.0 - ok / out.numel()
+
+
+@pytest.mark.parametrize("name", list(GOLDEN_CASES))
+def test_checker_agrees_with_the_fused_forward_and_the_oracle(name):
+    from flashmoe_b200.layer import MoELayer
+    w = GOLDEN_CASES[name]
+    lw, x = make_weights(w), make_tokens(w)
+    oracle_out, _ = oracle_layer(w, x=x, lw=lw, combine="element")   # the checker's combine arithmetic
+    layer = MoELayer(w, lw)
+    try:
+        out = layer.forward(x)
+        ref = reference_out(layer)
+        tol = REL_TOL[int(w.data_type)]
+        assert max_rel_err(out, ref) <= tol, max_rel_err(out, ref)
+        assert max_rel_err(ref.cpu(), oracle_out) <= tol, max_rel_err(ref.cpu(), oracle_out)
+        assert mismatch_fraction(out, ref) == 0.0
+    finally:
+        layer.close()
+
+
+@pytest.mark.parametrize("cfg,S", [("scout", 1024), ("scout", 8192), ("mixtral", 4096), ("qwen3", 8192),
+                                   ("deepseek_v3", 2048)])
+def test_checker_agrees_at_benchmark_shapes(cfg, S):
+    """Every element of the output at full size, against the unfused pipeline run on the same
+    routing table (tolerance of the benchmark description: 2e-2 of the largest magnitude)."""
+    import importlib.util
+    import os
+    from flashmoe_b200.layer import MoELayer
+    spec = importlib.util.spec_from_file_location(
+        "bench", os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "bench.py"))
+    bench = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(bench)
+    w = CONFIGS[cfg].scaled(tokens_per_rank=S)
+    lw = bench.device_weights(w, torch.device("cuda", 0), list(range(w.num_experts)))
+    layer = MoELayer(w, lw, 0, local_experts=range(w.num_experts))
+    try:
+        out = layer.forward(make_tokens(w))
+        ref = reference_out(layer)
+        assert torch.isfinite(out.float()).all()
+        assert max_rel_err(out, ref) <= 2e-2, max_rel_err(out, ref)
+        assert mismatch_fraction(out, ref) < 1e-4
+    finally:
+        layer.close()
