@@ -504,12 +504,15 @@ __device__ __forceinline__ void moe_forward_body(const MoeParams& p, const TmaMa
           const uint4* src = tok_base + static_cast<size_t>(token) * vecs;
           if constexpr (kPlanes == 1) {
             uint4* dst = reinterpret_cast<uint4*>(peer + p.lay.landing) + static_cast<size_t>(drow) * vecs;
-            for (int v0 = lane; v0 < vecs; v0 += 128) {   // four loads in flight per lane
-              uint4 x[4];
+            // A warp owns only a row or two, so its time is a chain of load -> store round trips:
+            // ten 16-byte loads in flight per lane make a 5120-element row two trips instead of five.
+            constexpr int kDepth = 10;
+            for (int v0 = lane; v0 < vecs; v0 += 32 * kDepth) {
+              uint4 x[kDepth];
 #pragma unroll
-              for (int u = 0; u < 4; ++u) if (v0 + 32 * u < vecs) x[u] = __ldg(src + v0 + 32 * u);
+              for (int u = 0; u < kDepth; ++u) if (v0 + 32 * u < vecs) x[u] = __ldg(src + v0 + 32 * u);
 #pragma unroll
-              for (int u = 0; u < 4; ++u) if (v0 + 32 * u < vecs) dst[v0 + 32 * u] = x[u];
+              for (int u = 0; u < kDepth; ++u) if (v0 + 32 * u < vecs) dst[v0 + 32 * u] = x[u];
             }
           } else {
             // fp32 row -> three BF16 planes at the owner (4 floats in, 3 x 8 bytes out)
