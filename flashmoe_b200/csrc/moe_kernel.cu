@@ -19,15 +19,15 @@
 //    and waits on the task's readiness counters itself.  Tickets are handed out in an order
 //    in which a task only ever waits on tasks with smaller tickets, so the kernel cannot
 //    deadlock as long as all CTAs are co-resident (grid <= SM count, one CTA per SM).
-//  * CTAs work in pairs (clusters of 2 on the two SMs of a TPC) on 256 x 256 output tiles with
-//    tcgen05.mma.cta_group::2: each CTA loads its own 128 rows of A and HALF of the B tile, so
-//    per SM the B bytes through shared memory are halved (the single-CTA form of this loop is
-//    bound by shared-memory bandwidth: TMA fill + UMMA operand reads).  Each CTA is
-//    warp-specialised: warp 0 = scheduler + TMA producer, warp 1 = UMMA issuer (leader CTA
-//    only) and TMEM owner, warps 2..5 = epilogue.  A 6-stage TMA->UMMA ring (32 KB per CTA per
-//    stage) and a double-buffered 2 x 256-column TMEM accumulator overlap loads, MMA and
-//    epilogue.  The leader's scheduler draws the ticket, waits for readiness and passes the
-//    ticket to the follower through distributed shared memory.
+//  * Each CTA is warp-specialised: warp 0 = scheduler + TMA producer, warp 1 = UMMA issuer and
+//    TMEM owner, warps 2..5 = epilogue.  By default every CTA works alone on 128 x 256 output
+//    tiles (tcgen05.mma.cta_group::1, M = 128, N = 256): a 4-stage TMA->UMMA ring of 48 KB stages
+//    (A tile 128 x 64, B tile 256 x 64) and a double-buffered 2 x 256-column TMEM accumulator
+//    overlap loads, MMA and epilogue.  A second form of the same body (opt-in) runs CTA pairs,
+//    clusters of 2 on the two SMs of a TPC, on 256 x 256 tiles with tcgen05.mma.cta_group::2:
+//    each CTA loads its own 128 rows of A and HALF of the B tile (6 stages of 32 KB), the leader's
+//    scheduler draws the ticket, waits for readiness and passes the ticket to the follower
+//    through distributed shared memory.
 //  * Gate and up projections are ONE UMMA of N = 256 (gate rows | up rows in the B tile);
 //    the SiLU-gate product is formed in the epilogue straight from TMEM.  The reference
 //    runs its main loop twice and parks the gate tile in shared memory
@@ -549,11 +549,10 @@ __device__ __forceinline__ void moe_forward_body(const MoeParams& p, const TmaMa
 
   stamp(3);
   // ---- expert GEMMs ---------------------------------------------------------------------
-  // Two CTAs (a cluster of 2, on the two SMs of one TPC) work on one 256 x 256 output tile:
-  // each loads its own 128 rows of A and its own half of the B tile, the leader issues
-  // tcgen05.mma.cta_group::2, each keeps its 128 rows of the accumulator in its own TMEM.  Per
-  // SM that halves the B bytes written to and read from shared memory per flop, which is what
-  // bounds the single-CTA form of this loop.
+  // Lone form: this CTA's 128 x 256 output tile, whole B tile per stage.  Pair form: two CTAs (a
+  // cluster of 2, on the two SMs of one TPC) work on one 256 x 256 output tile: each loads its own
+  // 128 rows of A and its own half of the B tile, the leader issues tcgen05.mma.cta_group::2, each
+  // keeps its 128 rows of the accumulator in its own TMEM.
   const int nk0 = p.H / kTileK, nk1 = p.I / kTileK;
   // plane pairs (A plane, B plane) per K block, smallest contributions first
   constexpr int kPairs = kPlanes == 1 ? 1 : 6;
