@@ -54,7 +54,7 @@ class Status(C.Structure):
 class Geometry(C.Structure):
     _fields_ = [(n, C.c_int32) for n in (
         "tile_m", "tile_n0", "tile_n1", "tile_k", "stages", "round_ec", "landing_rows", "grid",
-        "threads", "smem_bytes", "cta_pairs", "reserved")] + [("symm_bytes", C.c_int64),
+        "threads", "smem_bytes", "cta_pairs", "split_parts")] + [("symm_bytes", C.c_int64),
                                                                ("workspace_bytes", C.c_int64)]
 
 
@@ -73,6 +73,7 @@ SIGNATURES = {
     "fmoe_token_indices": (C.c_int, [C.c_void_p, C.POINTER(C.c_void_p)]),
     "fmoe_ctx_destroy": (C.c_int, [C.c_void_p, C.c_void_p]),
     "fmoe_forward": (C.c_int, [C.c_void_p, C.POINTER(ForwardArgsC), C.c_void_p]),
+    "fmoe_weights_changed": (C.c_int, [C.c_void_p]),
     "fmoe_router_create": (C.c_int, [C.POINTER(ModelDesc), C.c_int32, C.c_int32, C.c_void_p,
                                      C.POINTER(C.c_void_p)]),
     "fmoe_router_forward": (C.c_int, [C.c_void_p, C.c_void_p, C.POINTER(RouterArgsC), C.c_void_p]),

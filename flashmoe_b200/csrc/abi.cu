@@ -86,6 +86,7 @@ struct fmoe_ctx {
   char* peers[FMOE_MAX_WORLD] = {};     // mapped blocks (peers[rank] == symm)
   bool imported[FMOE_MAX_WORLD] = {};   // opened through IPC (must be closed)
   bool committed = false;
+  bool poisoned = false;                // a forward of this context ran out of a device-side wait
   char* work = nullptr;                 // private workspace, one allocation
   size_t work_bytes = 0;
   MoeParams params{};                   // everything but the per-forward pointers
@@ -113,6 +114,7 @@ struct fmoe_ctx {
   int planes = 1;                       // BF16 planes per GEMM operand (3 for fp32 layers)
   char* wsplit = nullptr;               // fp32 layers: BF16 planes of up | up_v | down
   size_t wsplit_up = 0, wsplit_up_v = 0, wsplit_down = 0;
+  const void* wsplit_src[3] = {nullptr, nullptr, nullptr};   // the weight set those planes were made from
 };
 
 struct fmoe_router {
@@ -163,10 +165,26 @@ namespace {
 struct Plan {
   int round_ec = 0, landing_rows = 0, max_mtiles = 0;
   SymmLayout lay{};
-  size_t w_y = 0, w_done = 0, w_ctl = 0, w_status = 0, w_trace = 0, w_table = 0, w_routes = 0, w_owner = 0,
-         w_lidx = 0, w_local = 0, work_bytes = 0;
+  size_t w_y = 0, w_split = 0, w_done = 0, w_split_done = 0, w_ctl = 0, w_status = 0, w_trace = 0, w_table = 0,
+         w_routes = 0, w_owner = 0, w_lidx = 0, w_local = 0, work_bytes = 0;
+  int split_parts = 1, split_tiles = 0;
   size_t weight_plane_bytes = 0;   // fp32 layers: the BF16 planes of up, up_v and down
 };
+
+// GEMM1 tiles of the closing wave are cut along K into this many tickets (FMOE_SPLIT_PARTS
+// overrides; 1 = never).  The count of cut tiles is one wave of the largest grid (one CTA per SM).
+constexpr int kSplitPartsDefault = 4;
+constexpr int kSplitTilesMax = 160;
+
+int split_parts_for(const fmoe_model_desc& m) {
+  int parts = kSplitPartsDefault;
+  if (const char* e = std::getenv("FMOE_SPLIT_PARTS")) parts = std::atoi(e);
+  if (const char* e = std::getenv("FMOE_PAIR")) if (std::atoi(e)) parts = 1;   // the CTA-pair form never cuts
+  const int nk1 = m.ffn_size / kTileK;
+  if (parts > 8) parts = 8;
+  if (parts < 2 || nk1 < 4 * parts) parts = 1;   // at least four K blocks per part
+  return parts;
+}
 
 Plan plan_sizes(const fmoe_model_desc& m, int W, int nLx) {
   Plan pl;
@@ -193,10 +211,14 @@ Plan plan_sizes(const fmoe_model_desc& m, int W, int nLx) {
   // private workspace
   size_t w = 0;
   pl.w_y = w; w = align_up(w + static_cast<size_t>(planes) * pl.landing_rows * I * 2, 1024);
+  pl.split_parts = split_parts_for(m);
+  pl.split_tiles = pl.split_parts > 1 ? kSplitTilesMax : 0;
+  pl.w_split = w; w = align_up(w + static_cast<size_t>(pl.split_tiles) * (pl.split_parts - 1) * kTileM * kUmmaN * sizeof(float), 1024);
   pl.w_done = w; w = align_up(w + sizeof(uint32_t) * pl.max_mtiles, 256);
+  pl.w_split_done = w; w = align_up(w + sizeof(uint32_t) * 4 * (pl.split_tiles + 1), 256);
   pl.w_ctl = w; w = align_up(w + 256, 256);   // ticket, done_ctas, abort, epoch
   pl.w_status = w; w = align_up(w + sizeof(fmoe_status), 256);
-  pl.w_trace = w; w = align_up(w + sizeof(unsigned long long) * 8 * 256, 256);
+  pl.w_trace = w; w = align_up(w + sizeof(unsigned long long) * kTraceSlots * 256, 256);
   pl.w_table = w; w = align_up(w + sizeof(TokenSlot) * E * pl.round_ec, 256);
   pl.w_routes = w; w = align_up(w + sizeof(Route) * S * k, 256);
   pl.w_owner = w; w = align_up(w + sizeof(int32_t) * E, 256);
@@ -358,11 +380,6 @@ int fmoe_ctx_create(const fmoe_model_desc* model, const fmoe_ep_desc* ep, void* 
   if (ce == cudaSuccess) ce = cudaMemcpyAsync(c->work + w_local, c->local_e.data(), sizeof(int32_t) * W * nLx, cudaMemcpyHostToDevice, st);
   if (ce == cudaSuccess) ce = cudaStreamSynchronize(st);
   if (ce == cudaSuccess) ce = moe_prepare_kernel(g.smem_bytes);
-  if (ce == cudaSuccess) {
-    // every device-side wait gives up after this long (default 2 s; FMOE_SPIN_LIMIT_MS overrides)
-    const char* lim = std::getenv("FMOE_SPIN_LIMIT_MS");
-    ce = set_spin_limit_ms(lim ? std::atof(lim) : 2000.0);
-  }
   if (ce != cudaSuccess) { free_ctx(c); return set_error(FMOE_ERR_CUDA, std::string("workspace set-up: ") + cudaGetErrorString(ce)); }
 
   MoeParams& p = c->params;
@@ -370,7 +387,13 @@ int fmoe_ctx_create(const fmoe_model_desc* model, const fmoe_ep_desc* ep, void* 
   p.W = W; p.rank = c->rank; p.nLx = nLx;
   p.gated = gated ? 1 : 0; p.act = model->act_type; p.ab_format = model->data_type == FMOE_DT_FP16 ? 0 : 1;
   p.elem_bytes = c->eb;
-  { const char* dbg = std::getenv("FMOE_DEBUG"); p.debug_flags = dbg ? std::atoi(dbg) : 0; }
+  {
+    // every device-side wait of this context gives up after this long (default 2 s)
+    const char* lim = std::getenv("FMOE_SPIN_LIMIT_MS");
+    p.spin_limit = spin_limit_cycles(lim ? std::atof(lim) : 2000.0, c->device);
+    const char* wh = std::getenv("FMOE_WITHHOLD_FLAGS");   // test hook: see MoeParams::withhold_flags
+    p.withhold_flags = (wh && std::atoi(wh)) ? 1 : 0;
+  }
   // Two forms of the GEMM loop exist: every CTA alone on a 128 x 256 tile (default), or CTA pairs
   // on 256 x 256 tiles with tcgen05.mma.cta_group::2 (FMOE_PAIR=1).  Measured on one B200 the pair
   // form gains 3-6 % per unit of MMA work on experts with many M tiles and loses more than that
@@ -381,13 +404,13 @@ int fmoe_ctx_create(const fmoe_model_desc* model, const fmoe_ep_desc* ep, void* 
     const char* force = std::getenv("FMOE_PAIR");
     if (force) p.pair = std::atoi(force) ? 1 : 0;
     g.cta_pairs = p.pair; g.stages = p.pair ? 6 : 4;
-    p.g1_mode = 0;   // half-width GEMM1 tickets measured no faster on one GPU; FMOE_G1=1|2 to try
-    const char* g1 = std::getenv("FMOE_G1");
-    if (g1) p.g1_mode = std::atoi(g1);
+    p.split_parts = pl.split_parts;
+    p.split_tiles = pl.split_parts > 1 ? (g.grid < kSplitTilesMax ? g.grid : kSplitTilesMax) : 0;
+    g.split_parts = p.split_parts;
   }
   p.tiles_n0 = (I + g.tile_n0 - 1) / g.tile_n0;
   p.tiles_n1 = (H + g.tile_n1 - 1) / g.tile_n1;
-  if (static_cast<long long>(S) * k * p.tiles_n1 * 2 >= (1LL << 31)) {
+  if (static_cast<long long>(S) * k * p.tiles_n1 >= (1LL << 31)) {
     free_ctx(c);
     return set_error(FMOE_ERR_UNSUPPORTED, "tokens_per_rank * top_k * ceil(H / 256) is too large for the 32-bit arrival counters");
   }
@@ -398,6 +421,8 @@ int fmoe_ctx_create(const fmoe_model_desc* model, const fmoe_ep_desc* ep, void* 
   p.lay = L;
   p.y = c->work + w_y;
   p.gemm0_done = reinterpret_cast<uint32_t*>(c->work + w_done);
+  p.split_scratch = reinterpret_cast<float*>(c->work + pl.w_split);
+  p.split_done = reinterpret_cast<uint32_t*>(c->work + pl.w_split_done);
   p.ticket = reinterpret_cast<uint32_t*>(c->work + w_ctl);
   p.done_ctas = reinterpret_cast<uint32_t*>(c->work + w_ctl + 64);
   p.abort_word = reinterpret_cast<uint32_t*>(c->work + w_ctl + 128);
@@ -505,7 +530,7 @@ int fmoe_debug_buffer(fmoe_ctx* ctx, int32_t which, void** ptr_out, size_t* byte
     case 2: *ptr_out = p.y; *bytes_out = static_cast<size_t>(ctx->planes) * p.landing_rows * p.I * 2; break;
     case 3: *ptr_out = ctx->symm + ctx->lay.ret; *bytes_out = static_cast<size_t>(p.S) * p.k * p.H * ctx->eb; break;
     case 4: *ptr_out = const_cast<Route*>(p.routes); *bytes_out = sizeof(Route) * p.S * p.k; break;
-    case 5: *ptr_out = p.trace; *bytes_out = sizeof(unsigned long long) * 8 * ctx->geo.grid; break;
+    case 5: *ptr_out = p.trace; *bytes_out = sizeof(unsigned long long) * kTraceSlots * ctx->geo.grid; break;
     default: return set_error(FMOE_ERR_INVALID_ARG, "unknown buffer id");
   }
   return FMOE_OK;
@@ -522,6 +547,9 @@ int fmoe_ctx_destroy(fmoe_ctx* ctx, void* stream) {
 int fmoe_forward(fmoe_ctx* ctx, const fmoe_forward_args* a, void* stream) {
   if (ctx == nullptr || a == nullptr) return set_error(FMOE_ERR_INVALID_ARG, "null argument");
   if (!ctx->committed) return set_error(FMOE_ERR_NOT_READY, "call fmoe_ctx_commit after importing every peer");
+  if (ctx->poisoned)
+    return set_error(FMOE_ERR_DEVICE_TIMEOUT, "an earlier forward of this context ran out of a device-side wait "
+                                              "(see fmoe_last_status); destroy the context and create a new one");
   const bool gated = ctx->params.gated != 0;
   if (a->tokens == nullptr || a->expert_counts == nullptr || a->local_expert_up == nullptr ||
       a->local_expert_down == nullptr || a->moe_out == nullptr || (gated && a->local_expert_up_v == nullptr))
@@ -534,11 +562,18 @@ int fmoe_forward(fmoe_ctx* ctx, const fmoe_forward_args* a, void* stream) {
   const void* up_v = gated ? a->local_expert_up_v : a->local_expert_up;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (ctx->planes == 3) {
-    const size_t n = static_cast<size_t>(p.nLx) * p.I * p.H;
-    FMOE_CUDA(launch_split_planes(static_cast<const float*>(a->local_expert_up), ctx->wsplit + ctx->wsplit_up, n, st));
-    if (gated)
-      FMOE_CUDA(launch_split_planes(static_cast<const float*>(a->local_expert_up_v), ctx->wsplit + ctx->wsplit_up_v, n, st));
-    FMOE_CUDA(launch_split_planes(static_cast<const float*>(a->local_expert_down), ctx->wsplit + ctx->wsplit_down, n, st));
+    // fp32 weights run as three BF16 planes.  The planes of the weight set seen last are kept, so a
+    // layer whose weights stay where they are pays for the split once, not per forward (a caller
+    // that rewrites weights in place calls fmoe_weights_changed).
+    if (ctx->wsplit_src[0] != a->local_expert_up || ctx->wsplit_src[1] != up_v ||
+        ctx->wsplit_src[2] != a->local_expert_down) {
+      const size_t n = static_cast<size_t>(p.nLx) * p.I * p.H;
+      FMOE_CUDA(launch_split_planes(static_cast<const float*>(a->local_expert_up), ctx->wsplit + ctx->wsplit_up, n, st));
+      if (gated)
+        FMOE_CUDA(launch_split_planes(static_cast<const float*>(a->local_expert_up_v), ctx->wsplit + ctx->wsplit_up_v, n, st));
+      FMOE_CUDA(launch_split_planes(static_cast<const float*>(a->local_expert_down), ctx->wsplit + ctx->wsplit_down, n, st));
+      ctx->wsplit_src[0] = a->local_expert_up; ctx->wsplit_src[1] = up_v; ctx->wsplit_src[2] = a->local_expert_down;
+    }
   } else {
     const fmoe_ctx::WeightMaps* hit = nullptr;
     for (const auto& wm : ctx->layer_maps)
@@ -572,7 +607,14 @@ int fmoe_last_status(fmoe_ctx* ctx, void* stream, fmoe_status* out) {
   if (ctx == nullptr || out == nullptr) return set_error(FMOE_ERR_INVALID_ARG, "null argument");
   FMOE_CUDA(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)));
   FMOE_CUDA(cudaMemcpy(out, ctx->params.status, sizeof(fmoe_status), cudaMemcpyDeviceToHost));
+  if (out->code != FMOE_OK) ctx->poisoned = true;
   return out->code;
+}
+
+int fmoe_weights_changed(fmoe_ctx* ctx) {
+  if (ctx == nullptr) return set_error(FMOE_ERR_INVALID_ARG, "null context");
+  ctx->wsplit_src[0] = ctx->wsplit_src[1] = ctx->wsplit_src[2] = nullptr;
+  return FMOE_OK;
 }
 
 int fmoe_router_create(const fmoe_model_desc* model, int32_t device_id, int32_t return_logits, void* stream,
@@ -604,6 +646,9 @@ int fmoe_router_create(const fmoe_model_desc* model, int32_t device_id, int32_t 
 
 int fmoe_router_forward(fmoe_router* router, fmoe_ctx* moe, const fmoe_router_args* a, void* stream) {
   if (router == nullptr || moe == nullptr || a == nullptr) return set_error(FMOE_ERR_INVALID_ARG, "null argument");
+  if (moe->poisoned)
+    return set_error(FMOE_ERR_DEVICE_TIMEOUT, "an earlier forward of this context ran out of a device-side wait "
+                                              "(see fmoe_last_status); destroy the context and create a new one");
   if (a->tokens == nullptr || a->weights == nullptr || a->expert_counts == nullptr)
     return set_error(FMOE_ERR_INVALID_ARG, "tokens, weights and expert_counts are required");
   if (router->return_logits && a->routing == nullptr)

@@ -34,6 +34,7 @@ constexpr int kTaskSlots = 4;    // task ring between the scheduler warp and its
 constexpr int kThreads = 192;    // warp 0 scheduler + TMA, warp 1 UMMA, warps 2..5 epilogue
 constexpr uint32_t kStageABytes = kTileM * kTileK * 2;        // 128 rows x 64 columns of 16-bit: 16 KB
 
+constexpr int kTraceSlots = 16;   // phase stamps per CTA
 constexpr uint32_t kMetaSrcShift = 26;  // landing meta = (source rank << 26) | return row
 
 // Offsets inside a rank's symmetric block (identical on every rank).
@@ -55,8 +56,10 @@ struct MoeParams {
   int gated, act, ab_format;  // ab_format: 0 fp16, 1 bf16 (fp32 layers run as BF16 planes)
   int elem_bytes;             // 2, or 4 for fp32 layers
   int pair;                   // 1: CTA pairs (cta_group::2), 0: every CTA alone
-  int g1_mode;                // GEMM1 half tiles (128 columns): 0 never, 1 in the closing segments, 2 always
-  int debug_flags;            // FMOE_DEBUG (environment, read at create): 1 = skip MMAs, 2 = skip loads (timing experiments; results are garbage), 4 = withhold the count flags (makes the first wait run out)
+  int withhold_flags;         // 1: never publish the count flags, so that the first wait runs out (a test of the bounded waits)
+  int split_parts;            // K parts per GEMM1 tile of the closing wave (1 = no tile is cut)
+  int split_tiles;            // how many GEMM1 tiles, counted from the end of the task order, are cut
+  long long spin_limit;       // SM clock ticks after which a device-side wait gives up
   int tiles_n0, tiles_n1;
   int landing_rows;
   int max_mtiles;
@@ -72,12 +75,14 @@ struct MoeParams {
   // private workspace
   void* y;                 // Element [landing_rows][I]  GEMM0 output
   uint32_t* gemm0_done;    // [max_mtiles] finished N0 tiles per M tile
+  float* split_scratch;    // [split_tiles][split_parts - 1][128 x 256] fp32 partial sums of the cut tiles
+  uint32_t* split_done;    // [split_tiles][4] parts parked, per tile and epilogue warp
   uint32_t* ticket;        // next task
   uint32_t* done_ctas;
   uint64_t* epoch;         // forward number, bumped by the last CTA to leave
   uint32_t* abort_word;
   fmoe_status* status;
-  unsigned long long* trace;  // [grid][8] %globaltimer stamps of the last forward, per CTA
+  unsigned long long* trace;  // [grid][kTraceSlots] %globaltimer stamps of the last forward, per CTA
 
   const TokenSlot* table;  // [E][round_ec]
   const Route* routes;     // [S][k]
@@ -108,7 +113,7 @@ struct RouterParams {
 cudaError_t launch_router(const RouterParams& p, cudaStream_t stream);
 size_t moe_smem_bytes(int W, int E, int nLx);
 cudaError_t moe_prepare_kernel(size_t smem);
-cudaError_t set_spin_limit_ms(double ms);   // bound of every device-side wait, this device
+long long spin_limit_cycles(double ms, int device);   // a wait limit in SM clock ticks
 cudaError_t launch_split_planes(const float* in, void* out, size_t n, cudaStream_t stream);
 cudaError_t launch_moe(const MoeParams& p, const CUtensorMap* maps, int grid, size_t smem,
                        cudaStream_t stream);

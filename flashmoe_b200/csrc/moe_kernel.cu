@@ -62,13 +62,16 @@ struct alignas(64) TmaMaps {
   CUtensorMap down;     // [nLx*H, I]          box 64 x 128
 };
 
-enum : int { kTaskGemm0 = 0, kTaskGemm1 = 1, kTaskStop = 2, kSegGemm1Half = 3 };
+enum : int { kTaskGemm0 = 0, kTaskGemm1 = 1, kTaskStop = 2 };
 
 // What one CTA of a pair does for one ticket: its own M tile (the leader takes the even tile of
 // the group, the follower the odd one) of the pair's 256 x 256 output tile.
 struct Task {
   int kind, lx, mt, row0, rows, n, m_in_expert, ticket;
-  int col0, ncols;   // GEMM1: first output column and width (256, or 128 for a half tile)
+  // GEMM1 tiles of the closing wave are cut along K into `nparts` tickets: part `part` covers K
+  // blocks [nk * part / nparts, nk * (part + 1) / nparts); `split_idx` numbers the tile among the
+  // split ones (its slot in the partial-sum scratch and in the part counters).
+  int part, nparts, split_idx;
 };
 
 struct Control {
@@ -80,7 +83,7 @@ struct Control {
   Task tasks[kTaskSlots];
   uint32_t tmem_base;
   uint32_t ok;            // cleared when a CTA-wide wait failed
-  int total_tasks, n_segs, send_rows, expected_ret, lag;
+  int total_tasks, n_segs, send_rows, class0_experts, expected_ret, lag;
   uint64_t epoch;
 };
 
@@ -97,20 +100,20 @@ __device__ __forceinline__ void fail(const MoeParams& p, int phase, long long de
 
 // Spin until *ctr >= want (acquire, system scope).  false = gave up.
 __device__ __forceinline__ bool wait_counter_sys(const uint32_t* ctr, uint32_t want,
-                                                 const MoeParams& p) {
+                                                 const WaitCtx& w) {
   if (ld_acquire_sys(ctr) >= want) return true;
   SpinGuard g;
   while (ld_acquire_sys(ctr) < want) {
-    if (g.expired(p.abort_word)) return ld_acquire_sys(ctr) >= want;
+    if (g.expired(w)) return ld_acquire_sys(ctr) >= want;
   }
   return true;
 }
 __device__ __forceinline__ bool wait_counter_gpu(const uint32_t* ctr, uint32_t want,
-                                                 const MoeParams& p) {
+                                                 const WaitCtx& w) {
   if (ld_acquire_gpu(ctr) >= want) return true;
   SpinGuard g;
   while (ld_acquire_gpu(ctr) < want) {
-    if (g.expired(p.abort_word)) return ld_acquire_gpu(ctr) >= want;
+    if (g.expired(w)) return ld_acquire_gpu(ctr) >= want;
   }
   return true;
 }
@@ -228,19 +231,22 @@ __device__ __forceinline__ float bias_at(const void* bias, size_t idx) {
 struct Tables {
   int* n;          // [W][E] rows rank s sends to expert e (clamped to EC)
   int* dst_row0;   // [E]    landing row at e's owner where THIS rank's rows for e start
-  int* send_pref;  // [E+1]  prefix of n[rank][*]
+  int* ord;        // [E]    send order: position -> expert (experts their owners work on first come first)
+  int* send_pref;  // [E+1]  rows this rank sends before send-order position i
   int* lx_base;    // [nLx]  landing row where local expert lx starts (multiple of 128)
   int* lx_rows;    // [nLx]  rows of local expert lx, all sources
   int* lx_mt0;     // [nLx+1] prefix of M tiles
   int* seg_first;  // [2 nLx + 1] first ticket of each segment of the task order
   int* seg_kind;   // [2 nLx]
   int* seg_lx;     // [2 nLx]
+  int* seg_whole;  // [2 nLx] GEMM1 segments: leading tickets that cover a whole tile (the rest are K parts)
   int* tot;        // [E]    rows expert e receives from all sources
+  int* tmp;        // [E]    scratch of the table construction
 };
 
 __host__ __device__ inline size_t tables_ints(int W, int E, int nLx) {
-  return static_cast<size_t>(W) * E + E + (E + 1) + nLx + nLx + (nLx + 1) + (2 * nLx + 1) +
-         2 * nLx + 2 * nLx + E;
+  return static_cast<size_t>(W) * E + E + E + (E + 1) + nLx + nLx + (nLx + 1) + (2 * nLx + 1) +
+         2 * nLx + 2 * nLx + 2 * nLx + E + E;
 }
 
 // kPair = true: CTA pairs on 256-row tile groups (experts with several M tiles; tensor-bound work).
@@ -265,6 +271,7 @@ __device__ __forceinline__ void moe_forward_body(const MoeParams& p, const TmaMa
     int* q = tab;
     tb.n = q; q += p.W * p.E;
     tb.dst_row0 = q; q += p.E;
+    tb.ord = q; q += p.E;
     tb.send_pref = q; q += p.E + 1;
     tb.lx_base = q; q += p.nLx;
     tb.lx_rows = q; q += p.nLx;
@@ -272,8 +279,11 @@ __device__ __forceinline__ void moe_forward_body(const MoeParams& p, const TmaMa
     tb.seg_first = q; q += 2 * p.nLx + 1;
     tb.seg_kind = q; q += 2 * p.nLx;
     tb.seg_lx = q; q += 2 * p.nLx;
-    tb.tot = q;
+    tb.seg_whole = q; q += 2 * p.nLx;
+    tb.tot = q; q += p.E;
+    tb.tmp = q;
   }
+  const WaitCtx wc{p.abort_word, p.spin_limit};
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   uint32_t pair_rank = 0;                         // 0 = leader of the CTA pair, 1 = follower
   if constexpr (kPair) pair_rank = cluster_ctarank();
@@ -310,15 +320,16 @@ __device__ __forceinline__ void moe_forward_body(const MoeParams& p, const TmaMa
   if constexpr (kPair) cluster_sync_all();   // the peer's barriers exist before anything arrives on them
   tc_fence_after_sync();
   // per-CTA phase stamps (%globaltimer, ns): 0 start, 1 counts of all ranks in, 2 tables built,
-  // 3 dispatch done, 4 last ticket (stop) drawn, 5 this CTA's last task finished, 6 returns all in,
-  // 7 combine done
-  auto stamp = [&](int i) {
-    if (tid == 0) {
-      unsigned long long t;
-      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-      p.trace[static_cast<size_t>(blockIdx.x) * 8 + i] = t;
-    }
+  // 3 this CTA's share of the dispatch done (its epilogue warps; the other warps are already in the
+  // GEMM loop), 4 last ticket (stop) drawn, 5 this CTA's last task finished, 6 returns all in,
+  // 7 combine done, 8 first operand stage of this CTA's first task landed (the first MMA can issue)
+  auto stamp_now = [&](int i) {   // called by one thread
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    p.trace[static_cast<size_t>(blockIdx.x) * kTraceSlots + i] = t;
   };
+  auto stamp = [&](int i) { if (tid == 0) stamp_now(i); };
+  if (tid == 0) p.trace[static_cast<size_t>(blockIdx.x) * kTraceSlots + 8] = 0;
   stamp(0);
   const uint64_t epoch = ctl->epoch;
   const uint64_t flag_val = epoch + 1;
@@ -331,6 +342,7 @@ __device__ __forceinline__ void moe_forward_body(const MoeParams& p, const TmaMa
     for (int i = tid; i < p.max_mtiles; i += kThreads) p.gemm0_done[i] = 0;
     uint32_t* arrived = reinterpret_cast<uint32_t*>(self + p.lay.disp_arrived);
     for (int i = tid; i < W * nLx; i += kThreads) arrived[i] = 0;
+    for (int i = tid; i < p.split_tiles * 4; i += kThreads) p.split_done[i] = 0;
     if (tid == 0) {
       *reinterpret_cast<uint32_t*>(self + p.lay.ret_arrived) = 0;
       *p.ticket = 0;
@@ -343,9 +355,10 @@ __device__ __forceinline__ void moe_forward_body(const MoeParams& p, const TmaMa
     }
     __threadfence_system();
     __syncthreads();
-    // (debug flag 4 withholds the flags: every CTA's wait below then runs out, which is how the
-    // tests exercise the bounded-wait and status path without faulting anything)
-    if (tid < W && !(p.debug_flags & 4)) {
+    // (a context created with FMOE_WITHHOLD_FLAGS=1 never publishes the flags: every CTA's wait
+    // below then runs out, which is how the tests exercise the bounded-wait and status path
+    // without faulting anything)
+    if (tid < W && !p.withhold_flags) {
       uint64_t* f = reinterpret_cast<uint64_t*>(p.peers[tid] + p.lay.cnt_flag);
       fence_acq_rel_sys();
       st_release_sys(f + parity * W + p.rank, flag_val);
@@ -356,7 +369,7 @@ __device__ __forceinline__ void moe_forward_body(const MoeParams& p, const TmaMa
     SpinGuard g;
     bool ok = true;
     while (ld_acquire_sys(f) != flag_val) {
-      if (g.expired(p.abort_word)) { ok = (ld_acquire_sys(f) == flag_val); break; }
+      if (g.expired(wc)) { ok = (ld_acquire_sys(f) == flag_val); break; }
     }
     if (!ok) { fail(p, FMOE_PHASE_COUNTS, tid); ctl->ok = 0; }
   }
@@ -414,16 +427,29 @@ __device__ __forceinline__ void moe_forward_body(const MoeParams& p, const TmaMa
     }
   }
   __syncthreads();
+  // Send order: the experts that are in the first half of their owner's local list come first
+  // (class 0), the others after them (class 1); inside a class ascending expert id.  Every warp
+  // sends its share of class 0 before its share of class 1, so the rows the owners' first GEMM0
+  // tickets wait for are on the wire first and the second half of the transfer overlaps compute.
+  auto first_class = [&](int e) { return 2 * p.lidx[e] < nLx ? 1 : 0; };
   if (ctl->ok && warp == 0) {
-    const int sp = warp_scan([&](int e) { return tb.n[p.rank * E + e]; },
-                             [&](int e, int v) { tb.send_pref[e] = v; }, E);
+    const int e0 = warp_scan(first_class, [&](int e, int v) { tb.tmp[e] = v; }, E);
+    __syncwarp();
+    for (int e = lane; e < E; e += 32) {
+      const int before = tb.tmp[e];
+      tb.ord[first_class(e) ? before : e0 + (e - before)] = e;
+    }
+    __syncwarp();
+    const int sp = warp_scan([&](int i) { return tb.n[p.rank * E + tb.ord[i]]; },
+                             [&](int i, int v) { tb.send_pref[i] = v; }, E);
     const int mt = warp_scan([&](int lx) { return (tb.lx_rows[lx] + kTileM - 1) / kTileM; },
                              [&](int lx, int v) { tb.lx_mt0[lx] = v; }, nLx);
     if (lane == 0) {
       tb.send_pref[E] = sp;
       tb.lx_mt0[nLx] = mt;
       ctl->send_rows = sp;
-      ctl->expected_ret = sp * p.tiles_n1 * 2;   // counted in half tiles (128 columns)
+      ctl->class0_experts = e0;
+      ctl->expected_ret = sp * p.tiles_n1;   // one count per returned row and N1 tile
       ctl->lag = nLx;
     }
   }
@@ -447,11 +473,16 @@ __device__ __forceinline__ void moe_forward_body(const MoeParams& p, const TmaMa
       const int s1 = i + lag;
       const int i1 = min(s1, nLx) + i + (s1 < nLx ? 1 : 0);                 // G1(i)
       tb.seg_first[i0] = groups * p.tiles_n0; tb.seg_kind[i0] = kTaskGemm0; tb.seg_lx[i0] = i;
-      // GEMM1 as half tiles (128 columns): finer tickets where they end the kernel (the segments
-      // emitted after the last GEMM0 segment), or everywhere (g1_mode 2); never in pair mode
-      const bool half = !kPair && (p.g1_mode == 2 || (p.g1_mode == 1 && i >= nLx - lag));
-      tb.seg_first[i1] = groups * p.tiles_n1 * (half ? 2 : 1);
-      tb.seg_kind[i1] = half ? kSegGemm1Half : kTaskGemm1; tb.seg_lx[i1] = i;
+      tb.seg_whole[i0] = groups * p.tiles_n0;
+      // The last `split_tiles` GEMM1 tiles of the task order (about one wave of CTAs) are cut along
+      // K into `split_parts` tickets each, so that the kernel ends on short tickets: `after` tiles
+      // follow this segment, so its last (split_tiles - after) tiles are cut.  Never in pair mode.
+      const int tiles = groups * p.tiles_n1;
+      const int after = (tb.lx_mt0[nLx] - tb.lx_mt0[i + 1]) * p.tiles_n1;   // kGroup == 1 when splitting
+      const int cut = (kPair || p.split_parts <= 1) ? 0 : max(0, min(tiles, p.split_tiles - after));
+      tb.seg_first[i1] = (tiles - cut) + cut * p.split_parts;
+      tb.seg_whole[i1] = tiles - cut;
+      tb.seg_kind[i1] = kTaskGemm1; tb.seg_lx[i1] = i;
     }
   }
   __syncthreads();
@@ -468,22 +499,22 @@ __device__ __forceinline__ void moe_forward_body(const MoeParams& p, const TmaMa
   stamp(2);
 
   // ---- dispatch: push this rank's routed rows to the experts' owners --------------------
-  if (ctl->ok) {
-    const int G = gridDim.x * (kThreads / 32);
-    const int gw = blockIdx.x * (kThreads / 32) + warp;
-    const long long R = ctl->send_rows;
-    int q = static_cast<int>(R * gw / G);
-    const int q_end = static_cast<int>(R * (gw + 1) / G);
+  // Done by the four epilogue warps of every CTA, on their way into the epilogue loop; warps 0 and
+  // 1 are already drawing tickets and loading weights.  A GEMM0 ticket waits for the rows of its
+  // own M tile only (per source, on disp_arrived) and the dispatch depends on no ticket, so the
+  // order stays deadlock-free; the first epilogue is due one whole main loop after the first MMA.
+  auto dispatch_range = [&](int q, const int q_end) {
     const int vecs = p.H * EB / 16;
     const uint4* tok_base = static_cast<const uint4*>(p.tokens);
     while (q < q_end) {
-      int lo = 0, hi = E;  // largest e with send_pref[e] <= q
+      int lo = 0, hi = E;  // largest position with send_pref[position] <= q
       while (hi - lo > 1) {
         const int mid = (lo + hi) >> 1;
         if (tb.send_pref[mid] <= q) lo = mid; else hi = mid;
       }
-      const int e = lo;
-      const int run_end = min(q_end, tb.send_pref[e + 1]);
+      const int e = tb.ord[lo];
+      const int first = tb.send_pref[lo];
+      const int run_end = min(q_end, tb.send_pref[lo + 1]);
       const int r = p.owner[e], lx = p.lidx[e];
       char* peer = p.peers[r];
       const int run_start = q;
@@ -493,14 +524,14 @@ __device__ __forceinline__ void moe_forward_body(const MoeParams& p, const TmaMa
         const int batch = min(32, run_end - q);
         uint32_t my_token = 0, my_choice = 0;
         if (lane < batch) {
-          my_token = p.table[static_cast<size_t>(e) * p.round_ec + (q - tb.send_pref[e]) + lane].token;
+          my_token = p.table[static_cast<size_t>(e) * p.round_ec + (q - first) + lane].token;
           for (int c = 0; c < p.k; ++c)
             if (p.routes[static_cast<size_t>(my_token) * p.k + c].expert == e) { my_choice = c; break; }
         }
         for (int i = 0; i < batch; ++i) {
           const uint32_t token = __shfl_sync(0xffffffffu, my_token, i);
           const uint32_t choice = __shfl_sync(0xffffffffu, my_choice, i);
-          const int drow = tb.dst_row0[e] + (q - tb.send_pref[e]) + i;
+          const int drow = tb.dst_row0[e] + (q - first) + i;
           const uint4* src = tok_base + static_cast<size_t>(token) * vecs;
           if constexpr (kPlanes == 1) {
             uint4* dst = reinterpret_cast<uint4*>(peer + p.lay.landing) + static_cast<size_t>(drow) * vecs;
@@ -545,9 +576,8 @@ __device__ __forceinline__ void moe_forward_body(const MoeParams& p, const TmaMa
         red_add_release_sys(reinterpret_cast<uint32_t*>(peer + p.lay.disp_arrived) + p.rank * nLx + lx,
                             static_cast<uint32_t>(sent));
     }
-  }
+  };
 
-  stamp(3);
   // ---- expert GEMMs ---------------------------------------------------------------------
   // Lone form: this CTA's 128 x 256 output tile, whole B tile per stage.  Pair form: two CTAs (a
   // cluster of 2, on the two SMs of one TPC) work on one 256 x 256 output tile: each loads its own
@@ -570,21 +600,23 @@ __device__ __forceinline__ void moe_forward_body(const MoeParams& p, const TmaMa
       if (tb.seg_first[mid] <= ticket) lo = mid; else hi = mid;
     }
     const int lx = tb.seg_lx[lo];
-    const int idx = ticket - tb.seg_first[lo];
+    int idx = ticket - tb.seg_first[lo];     // tile of the segment, N-major
     const int mts = tb.lx_mt0[lx + 1] - tb.lx_mt0[lx];
     const int groups = (mts + kGroup - 1) / kGroup;
     t.kind = tb.seg_kind[lo];
     t.lx = lx;
+    t.nparts = 1;
+    const int whole = tb.seg_whole[lo];
+    if (idx >= whole) {                      // a K part of one of the segment's last tiles
+      const int j = idx - whole;
+      idx = whole + j / p.split_parts;
+      t.part = j - (idx - whole) * p.split_parts;
+      t.nparts = p.split_parts;
+      const int after = (tb.lx_mt0[nLx] - tb.lx_mt0[lx + 1]) * p.tiles_n1;
+      t.split_idx = after + (groups * p.tiles_n1 - 1 - idx);
+    }
     const int n2 = idx / groups;
     t.n = n2;
-    t.col0 = n2 * kUmmaN;
-    t.ncols = kUmmaN;
-    if (t.kind == kSegGemm1Half) {
-      t.kind = kTaskGemm1;
-      t.n = n2 >> 1;
-      t.col0 = n2 * (kUmmaN / 2);
-      t.ncols = kUmmaN / 2;
-    }
     t.m_in_expert = kGroup * (idx - n2 * groups) + static_cast<int>(pair_rank);
     t.mt = tb.lx_mt0[lx] + t.m_in_expert;
     t.row0 = tb.lx_base[lx] + t.m_in_expert * kTileM;
@@ -606,7 +638,7 @@ __device__ __forceinline__ void moe_forward_body(const MoeParams& p, const TmaMa
           ticket = next_ticket >= 0 ? next_ticket : static_cast<int>(atomicAdd(p.ticket, 1u));
           next_ticket = -1;
         } else {
-          if (!mbar_wait_cluster(&ctl->pair_full[tslot], ring_par, p.abort_word)) {
+          if (!mbar_wait_cluster(&ctl->pair_full[tslot], ring_par, wc)) {
             fail(p, FMOE_PHASE_TASK, -3); ok = false; break;
           }
           ticket = static_cast<int>(ctl->pair_ticket[tslot]);
@@ -623,7 +655,7 @@ __device__ __forceinline__ void moe_forward_body(const MoeParams& p, const TmaMa
             for (int s = 0; s < W && ok; ++s) {
               const int ns = tb.n[s * E + e];
               if (ns > 0 && off < hi_row && off + ns > lo_row) {
-                if (!wait_counter_sys(arrived + s * nLx + t.lx, static_cast<uint32_t>(ns), p)) {
+                if (!wait_counter_sys(arrived + s * nLx + t.lx, static_cast<uint32_t>(ns), wc)) {
                   fail(p, FMOE_PHASE_DISPATCH_ARRIVAL, s); ok = false;
                 }
               }
@@ -633,21 +665,21 @@ __device__ __forceinline__ void moe_forward_body(const MoeParams& p, const TmaMa
             const int mts = tb.lx_mt0[t.lx + 1] - tb.lx_mt0[t.lx];
             for (int q = 0; q < kGroup && ok; ++q) {
               if (t.m_in_expert + q >= mts) break;
-              if (!wait_counter_gpu(p.gemm0_done + t.mt + q, static_cast<uint32_t>(4 * p.tiles_n0), p)) {
+              if (!wait_counter_gpu(p.gemm0_done + t.mt + q, static_cast<uint32_t>(4 * p.tiles_n0), wc)) {
                 fail(p, FMOE_PHASE_GEMM0_DONE, t.mt + q); ok = false;
               }
             }
           }
           if (!ok) break;
           if constexpr (kPair) {
-            if (!mbar_wait_cluster(&ctl->pair_empty[tslot], ring_par ^ 1, p.abort_word)) {
+            if (!mbar_wait_cluster(&ctl->pair_empty[tslot], ring_par ^ 1, wc)) {
               fail(p, FMOE_PHASE_TASK, -4); ok = false; break;
             }
             st_cluster_u32(map_to_cta(&ctl->pair_ticket[tslot], 1), static_cast<uint32_t>(ticket));
             mbar_arrive_cluster(map_to_cta(&ctl->pair_full[tslot], 1));
           }
         }
-        if (!mbar_wait(&ctl->task_empty[tslot], ring_par ^ 1, p.abort_word)) {
+        if (!mbar_wait(&ctl->task_empty[tslot], ring_par ^ 1, wc)) {
           fail(p, FMOE_PHASE_TASK, ticket); ok = false; break;
         }
         ctl->tasks[tslot] = t;
@@ -667,40 +699,35 @@ __device__ __forceinline__ void moe_forward_body(const MoeParams& p, const TmaMa
           if (p.gated) { brow0 = t.lx * p.I + t.n * 128; brow1 = brow0; }
           else { brow0 = t.lx * p.I + t.n * 256; brow1 = brow0 + 128; }
         } else {
-          brow0 = t.lx * p.H + t.col0; brow1 = brow0 + 128;
+          brow0 = t.lx * p.H + t.n * kUmmaN; brow1 = brow0 + 128;
         }
-        const bool half_b = !g0 && t.ncols == kUmmaN / 2;   // only the first 128 rows of the B tile
         const CUtensorMap* map_b = leader ? map_b0 : map_b1;
         const int brow = leader ? brow0 : brow1;
         const int b_plane_rows = g0 ? nLx * p.I : nLx * p.H;   // rows of one BF16 plane of the weights
-        for (int kb = 0; kb < nk && ok; ++kb) {
+        const int kb_begin = nk * t.part / t.nparts, kb_end = nk * (t.part + 1) / t.nparts;
+        for (int kb = kb_begin; kb < kb_end && ok; ++kb) {
           // the next ticket is drawn while the last stages of this task are still being consumed,
           // so the atomic's round trip is off the path between two tasks (not earlier: a CTA
           // holding a spare ticket for long would unbalance the closing wave)
-          if (leader && kb == max(0, nk - 6)) next_ticket = static_cast<int>(atomicAdd(p.ticket, 1u));
+          if (leader && kb == max(kb_begin, kb_end - 6)) next_ticket = static_cast<int>(atomicAdd(p.ticket, 1u));
           for (int pp = 0; pp < kPairs; ++pp, ++fill) {
             const int pa = kPlanes == 1 ? 0 : kPairA[pp], pb = kPlanes == 1 ? 0 : kPairB[pp];
             const uint32_t s = fill % NS;
-            if (!mbar_wait_cluster(&ctl->empty[s], ((fill / NS) & 1) ^ 1, p.abort_word)) {
+            if (!mbar_wait_cluster(&ctl->empty[s], ((fill / NS) & 1) ^ 1, wc)) {
               fail(p, FMOE_PHASE_PIPE_EMPTY, ticket); ok = false; break;
             }
             uint8_t* sa = stages + s * STAGE;
             uint8_t* sb = sa + SA;
-            if (p.debug_flags & 2) {   // timing experiment: no loads, the MMAs chew on stale tiles
-              if (leader) mbar_arrive(&ctl->full[s]);
-              continue;
-            }
             if constexpr (kPair) {
               // the leader's barrier counts the bytes of both CTAs
               if (leader) mbar_expect_tx(&ctl->full[s], 2 * STAGE);
               tma_load_2d_pair(sa, map_a, &ctl->full[s], kb * kTileK, t.row0 + pa * p.landing_rows);
               tma_load_2d_pair(sb, map_b, &ctl->full[s], kb * kTileK, brow + pb * b_plane_rows);
             } else {
-              mbar_expect_tx(&ctl->full[s], half_b ? SA + SB / 2 : STAGE);
+              mbar_expect_tx(&ctl->full[s], STAGE);
               tma_load_2d(sa, map_a, &ctl->full[s], kb * kTileK, t.row0 + pa * p.landing_rows);
               tma_load_2d(sb, map_b0, &ctl->full[s], kb * kTileK, brow0 + pb * b_plane_rows);
-              if (!half_b)
-                tma_load_2d(sb + SB / 2, map_b1, &ctl->full[s], kb * kTileK, brow1 + pb * b_plane_rows);
+              tma_load_2d(sb + SB / 2, map_b1, &ctl->full[s], kb * kTileK, brow1 + pb * b_plane_rows);
             }
           }
         }
@@ -721,20 +748,19 @@ __device__ __forceinline__ void moe_forward_body(const MoeParams& p, const TmaMa
     }
   } else if (ctl->ok && warp == 1) {
     if (lane == 0 && leader) {
-      const uint32_t idesc_full = umma_idesc_f16(Cvt<T>::kFormat, kGroup * kTileM, kUmmaN);
-      const uint32_t idesc_half = umma_idesc_f16(Cvt<T>::kFormat, kGroup * kTileM, kUmmaN / 2);
+      const uint32_t idesc = umma_idesc_f16(Cvt<T>::kFormat, kGroup * kTileM, kUmmaN);
       uint32_t fill = 0, tslot = 0, acc_it = 0;
       for (uint32_t it = 0;; ++it, tslot = (tslot + 1) % kTaskSlots) {
-        if (!mbar_wait(&ctl->task_full[tslot], (it / kTaskSlots) & 1, p.abort_word)) {
+        if (!mbar_wait(&ctl->task_full[tslot], (it / kTaskSlots) & 1, wc)) {
           fail(p, FMOE_PHASE_TASK, -1); break;
         }
         const Task t = ctl->tasks[tslot];
         mbar_arrive(&ctl->task_empty[tslot]);
         if (t.kind == kTaskStop) break;
-        const int nk = (t.kind == kTaskGemm0 ? nk0 : nk1) * kPairs;
-        const uint32_t idesc = (t.kind == kTaskGemm1 && t.ncols == kUmmaN / 2) ? idesc_half : idesc_full;
+        const int nkb = t.kind == kTaskGemm0 ? nk0 : nk1;   // this ticket's K blocks: the task's, or one part of them
+        const int nk = (nkb * (t.part + 1) / t.nparts - nkb * t.part / t.nparts) * kPairs;
         const uint32_t buf = acc_it % kBufs;
-        if (!mbar_wait_cluster(&ctl->acc_empty[buf], ((acc_it / kBufs) & 1) ^ 1, p.abort_word)) {
+        if (!mbar_wait_cluster(&ctl->acc_empty[buf], ((acc_it / kBufs) & 1) ^ 1, wc)) {
           fail(p, FMOE_PHASE_TMEM_EMPTY, t.mt); break;
         }
         tc_fence_after_sync();
@@ -743,23 +769,22 @@ __device__ __forceinline__ void moe_forward_body(const MoeParams& p, const TmaMa
         bool ok = true;
         for (int kb = 0; kb < nk; ++kb, ++fill) {
           const uint32_t s = fill % NS;
-          if (!mbar_wait_cluster(&ctl->full[s], (fill / NS) & 1, p.abort_word)) {
+          if (!mbar_wait_cluster(&ctl->full[s], (fill / NS) & 1, wc)) {
             fail(p, FMOE_PHASE_PIPE_FULL, t.mt); ok = false; break;
           }
           tc_fence_after_sync();
+          if (fill == 0) stamp_now(8);
           const uint32_t a_addr = smem_u32(stages + s * STAGE);
           const uint32_t b_addr = a_addr + SA;
           // fp32 layers: the last pair of every K block is the leading one (planes 0 x 0)
           const bool lead = kPlanes == 1 || (kb % kPairs) == kPairs - 1;
           const uint32_t d = lead ? d_tmem : d_corr;
           const bool first = lead ? (kb < kPairs) : (kb == 0);
-          if (!(p.debug_flags & 1)) {   // flag 1 = timing experiment: loads only, no MMAs
 #pragma unroll
-            for (int k = 0; k < kTileK / 16; ++k) {
-              const uint64_t da = umma_desc_sw128(a_addr + k * 32), db = umma_desc_sw128(b_addr + k * 32);
-              if constexpr (kPair) umma_f16_pair(d, da, db, idesc, (!first || k > 0) ? 1u : 0u);
-              else umma_f16(d, da, db, idesc, (!first || k > 0) ? 1u : 0u);
-            }
+          for (int k = 0; k < kTileK / 16; ++k) {
+            const uint64_t da = umma_desc_sw128(a_addr + k * 32), db = umma_desc_sw128(b_addr + k * 32);
+            if constexpr (kPair) umma_f16_pair(d, da, db, idesc, (!first || k > 0) ? 1u : 0u);
+            else umma_f16(d, da, db, idesc, (!first || k > 0) ? 1u : 0u);
           }
           if constexpr (kPair) umma_commit_pair(&ctl->empty[s], 3);    // frees the stage in both CTAs
           else umma_commit(&ctl->empty[s]);
@@ -772,6 +797,18 @@ __device__ __forceinline__ void moe_forward_body(const MoeParams& p, const TmaMa
       }
     }
   } else if (ctl->ok) {
+    {
+      // this warp's share of the rows to send: its slice of class 0, then its slice of class 1
+      const int G = gridDim.x * 4;
+      const int gw = blockIdx.x * 4 + (warp - 2);
+      const long long R0 = tb.send_pref[ctl->class0_experts], R1 = ctl->send_rows - R0;
+#pragma unroll 1
+      for (int c = 0; c < 2; ++c) {
+        const long long base = c ? R0 : 0, n = c ? R1 : R0;
+        dispatch_range(static_cast<int>(base + n * gw / G), static_cast<int>(base + n * (gw + 1) / G));
+      }
+      if (warp == 2 && lane == 0) stamp_now(3);
+    }
     // epilogue warps: TMEM lane quadrant = warp id mod 4; this CTA's 128 rows of the pair's tile
     const int quad = warp & 3;
     const int row_in_tile = quad * 32 + lane;
@@ -779,7 +816,7 @@ __device__ __forceinline__ void moe_forward_body(const MoeParams& p, const TmaMa
     if constexpr (kPair) acc_empty_leader = map_to_cta(&ctl->acc_empty[0], 0);
     uint32_t tslot = 0, acc_it = 0;
     for (uint32_t it = 0;; ++it, tslot = (tslot + 1) % kTaskSlots) {
-      if (!mbar_wait(&ctl->task_full[tslot], (it / kTaskSlots) & 1, p.abort_word)) {
+      if (!mbar_wait(&ctl->task_full[tslot], (it / kTaskSlots) & 1, wc)) {
         fail(p, FMOE_PHASE_TASK, -2); break;
       }
       const Task t = ctl->tasks[tslot];
@@ -787,7 +824,7 @@ __device__ __forceinline__ void moe_forward_body(const MoeParams& p, const TmaMa
       if (lane == 0) mbar_arrive(&ctl->task_empty[tslot]);
       if (t.kind == kTaskStop) break;
       const uint32_t buf = acc_it % kBufs;
-      if (!mbar_wait_cluster(&ctl->acc_full[buf], (acc_it / kBufs) & 1, p.abort_word)) {
+      if (!mbar_wait_cluster(&ctl->acc_full[buf], (acc_it / kBufs) & 1, wc)) {
         fail(p, FMOE_PHASE_TMEM_FULL, t.mt); break;
       }
       tc_fence_after_sync();
@@ -873,16 +910,14 @@ __device__ __forceinline__ void moe_forward_body(const MoeParams& p, const TmaMa
         // every lane's stores happen before the barrier, the barrier before lane 0's release
         __syncwarp();
         if (lane == 0 && t.rows > 0) red_add_release_gpu(p.gemm0_done + t.mt, 1u);
-      } else {
-        uint32_t meta = 0;
-        if (valid) meta = __ldcg(reinterpret_cast<const uint32_t*>(self + p.lay.landing_meta) + row);
-        const int src = static_cast<int>(meta >> kMetaSrcShift);
-        const uint32_t ret_row = meta & ((1u << kMetaSrcShift) - 1);
-        char* orow = p.peers[valid ? src : p.rank] + p.lay.ret + static_cast<size_t>(ret_row) * p.H * EB;
-        const int col_base = t.col0;
-        const int chunks = t.ncols / 32;
+      } else if (t.nparts > 1 && t.part < t.nparts - 1) {
+        // One K part of a tile of the closing wave, not the last: park the fp32 partial sums (chunk
+        // c, column i, row r at [(32 c + i) * 128 + r], so that a warp writes whole lines) and
+        // count this warp's quarter in.
+        float* part = p.split_scratch +
+                      (static_cast<size_t>(t.split_idx) * (p.split_parts - 1) + t.part) * (kTileM * kUmmaN);
 #pragma unroll 1
-        for (int c = 0; c < chunks; ++c) {
+        for (int c = 0; c < kUmmaN / 32; ++c) {
           uint32_t a[32];
           __syncwarp();
           tmem_ld_32x32(taddr + c * 32, a);
@@ -894,14 +929,70 @@ __device__ __forceinline__ void moe_forward_body(const MoeParams& p, const TmaMa
 #pragma unroll
             for (int i = 0; i < 32; ++i) a[i] = __float_as_uint(__uint_as_float(a[i]) + __uint_as_float(ca[i]));
           }
-          if (c == chunks - 1) release_acc();
-          const int col0 = col_base + c * 32;
-          if (valid && col0 < p.H) {
-            float o[32];
+          if (c == kUmmaN / 32 - 1) release_acc();
 #pragma unroll
-            for (int i = 0; i < 32; ++i)
-              o[i] = __uint_as_float(a[i]) + bias_at<T>(p.bias_down, static_cast<size_t>(t.lx) * p.H + col0 + i);
-            store_result32<T>(orow, col0, o);
+          for (int i = 0; i < 32; ++i) __stcg(part + (c * 32 + i) * kTileM + row_in_tile, __uint_as_float(a[i]));
+        }
+        // every lane's stores happen before the barrier, the barrier before lane 0's release
+        __syncwarp();
+        if (lane == 0) red_add_release_gpu(p.split_done + t.split_idx * 4 + quad, 1u);
+      } else {
+        uint32_t meta = 0;
+        if (valid) meta = __ldcg(reinterpret_cast<const uint32_t*>(self + p.lay.landing_meta) + row);
+        const int src = static_cast<int>(meta >> kMetaSrcShift);
+        const uint32_t ret_row = meta & ((1u << kMetaSrcShift) - 1);
+        char* orow = p.peers[valid ? src : p.rank] + p.lay.ret + static_cast<size_t>(ret_row) * p.H * EB;
+        const int col_base = t.n * kUmmaN;
+        // The last K part of a split tile adds the parked partial sums of the parts before it, in
+        // part order, and finishes the tile.  Those parts hold smaller tickets, so waiting for them
+        // here keeps the task order deadlock-free; they were drawn at about the same time.
+        const float* parts = nullptr;
+        if (t.nparts > 1) {
+          parts = p.split_scratch + static_cast<size_t>(t.split_idx) * (p.split_parts - 1) * (kTileM * kUmmaN);
+          bool ready = true;
+          if (lane == 0)
+            ready = wait_counter_gpu(p.split_done + t.split_idx * 4 + quad, static_cast<uint32_t>(t.nparts - 1), wc);
+          ready = __shfl_sync(0xffffffffu, ready ? 1 : 0, 0) != 0;
+          if (!ready) { if (lane == 0) fail(p, FMOE_PHASE_SPLIT_PARTS, t.mt); break; }
+        }
+#pragma unroll 1
+        for (int c = 0; c < kUmmaN / 32; ++c) {
+          uint32_t a[32];
+          __syncwarp();
+          tmem_ld_32x32(taddr + c * 32, a);
+          tmem_ld_wait();
+          if constexpr (kPlanes == 3) {
+            uint32_t ca[32];
+            tmem_ld_32x32(taddr + kUmmaN + c * 32, ca);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) a[i] = __float_as_uint(__uint_as_float(a[i]) + __uint_as_float(ca[i]));
+          }
+          if (c == kUmmaN / 32 - 1) release_acc();
+          const int col0 = col_base + c * 32;
+          if (col0 < p.H) {
+            float o[32];
+            if (parts != nullptr) {
+              const float* q0 = parts + c * 32 * kTileM + row_in_tile;
+#pragma unroll
+              for (int i = 0; i < 32; ++i) o[i] = __ldcg(q0 + i * kTileM);
+              for (int pp = 1; pp < t.nparts - 1; ++pp) {
+                const float* qp = q0 + static_cast<size_t>(pp) * (kTileM * kUmmaN);
+#pragma unroll
+                for (int i = 0; i < 32; ++i) o[i] = __fadd_rn(o[i], __ldcg(qp + i * kTileM));
+              }
+#pragma unroll
+              for (int i = 0; i < 32; ++i) o[i] = __fadd_rn(o[i], __uint_as_float(a[i]));
+            } else {
+#pragma unroll
+              for (int i = 0; i < 32; ++i) o[i] = __uint_as_float(a[i]);
+            }
+            if (valid) {
+#pragma unroll
+              for (int i = 0; i < 32; ++i)
+                o[i] += bias_at<T>(p.bias_down, static_cast<size_t>(t.lx) * p.H + col0 + i);
+              store_result32<T>(orow, col0, o);
+            }
           }
         }
         __syncwarp();
@@ -910,7 +1001,7 @@ __device__ __forceinline__ void moe_forward_body(const MoeParams& p, const TmaMa
           const unsigned b = __ballot_sync(0xffffffffu, valid && src == s);
           if (lane == 0 && b != 0)
             red_add_release_sys(reinterpret_cast<uint32_t*>(p.peers[s] + p.lay.ret_arrived),
-                                static_cast<uint32_t>(__popc(b)) * static_cast<uint32_t>(t.ncols / 128));
+                                static_cast<uint32_t>(__popc(b)));
         }
       }
       ++acc_it;
@@ -924,7 +1015,7 @@ __device__ __forceinline__ void moe_forward_body(const MoeParams& p, const TmaMa
   stamp(5);
   if (tid == 0 && ctl->ok && *reinterpret_cast<volatile uint32_t*>(p.abort_word) == 0) {
     const uint32_t* ra = reinterpret_cast<const uint32_t*>(self + p.lay.ret_arrived);
-    if (!wait_counter_sys(ra, static_cast<uint32_t>(ctl->expected_ret), p)) {
+    if (!wait_counter_sys(ra, static_cast<uint32_t>(ctl->expected_ret), wc)) {
       fail(p, FMOE_PHASE_RETURN_ARRIVAL, ctl->expected_ret);
       ctl->ok = 0;
     }
@@ -1077,13 +1168,10 @@ __global__ void split_planes_kernel(const float* __restrict__ in, unsigned short
 }
 }  // namespace
 
-cudaError_t set_spin_limit_ms(double ms) {
-  int dev = 0, khz = 0;
-  cudaError_t e = cudaGetDevice(&dev);
-  if (e == cudaSuccess) e = cudaDeviceGetAttribute(&khz, cudaDevAttrClockRate, dev);
-  if (e != cudaSuccess) return e;
-  const long long cycles = static_cast<long long>(ms * static_cast<double>(khz));
-  return cudaMemcpyToSymbol(ptx::g_spin_limit_cycles, &cycles, sizeof(cycles));
+long long spin_limit_cycles(double ms, int device) {
+  int khz = 0;
+  if (cudaDeviceGetAttribute(&khz, cudaDevAttrClockRate, device) != cudaSuccess || khz <= 0) khz = 2000000;
+  return static_cast<long long>(ms * static_cast<double>(khz));
 }
 
 cudaError_t launch_split_planes(const float* in, void* out, size_t n, cudaStream_t stream) {
@@ -1095,21 +1183,36 @@ cudaError_t launch_split_planes(const float* in, void* out, size_t n, cudaStream
   return cudaGetLastError();
 }
 
+// The kernel's CTAs wait on one another (count flags, arrival counters, tickets), so all of them
+// must be resident at once.  A cooperative launch makes that a guarantee: the grid starts only
+// when every CTA has an SM, whatever else the device is running, and a grid that could never fit
+// is refused at launch instead of timing out in its first wait.
 cudaError_t launch_moe(const MoeParams& p, const CUtensorMap* maps, int grid, size_t smem,
                        cudaStream_t stream) {
   TmaMaps m;
   m.landing = maps[0]; m.y = maps[1]; m.up = maps[2]; m.up_v = maps[3]; m.down = maps[4];
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeCooperative;
+  attr[0].val.cooperative = 1;
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(static_cast<unsigned>(grid));
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaError_t e;
   if (p.pair) {
-    if (p.elem_bytes == 4) moe_forward_kernel_pair<float><<<grid, kThreads, smem, stream>>>(p, m);
-    else if (p.ab_format == 1) moe_forward_kernel_pair<__nv_bfloat16><<<grid, kThreads, smem, stream>>>(p, m);
-    else moe_forward_kernel_pair<__half><<<grid, kThreads, smem, stream>>>(p, m);
+    if (p.elem_bytes == 4) e = cudaLaunchKernelEx(&cfg, moe_forward_kernel_pair<float>, p, m);
+    else if (p.ab_format == 1) e = cudaLaunchKernelEx(&cfg, moe_forward_kernel_pair<__nv_bfloat16>, p, m);
+    else e = cudaLaunchKernelEx(&cfg, moe_forward_kernel_pair<__half>, p, m);
   } else {
-    if (p.elem_bytes == 4) moe_forward_kernel<float><<<grid, kThreads, smem, stream>>>(p, m);
-    else if (p.ab_format == 1) moe_forward_kernel<__nv_bfloat16><<<grid, kThreads, smem, stream>>>(p, m);
-    else moe_forward_kernel<__half><<<grid, kThreads, smem, stream>>>(p, m);
+    if (p.elem_bytes == 4) e = cudaLaunchKernelEx(&cfg, moe_forward_kernel<float>, p, m);
+    else if (p.ab_format == 1) e = cudaLaunchKernelEx(&cfg, moe_forward_kernel<__nv_bfloat16>, p, m);
+    else e = cudaLaunchKernelEx(&cfg, moe_forward_kernel<__half>, p, m);
   }
   ++g_launches;
-  return cudaGetLastError();
+  return e;
 }
 
 }  // namespace fmoe

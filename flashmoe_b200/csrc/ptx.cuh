@@ -14,24 +14,28 @@ __device__ __forceinline__ uint32_t smem_u32(const void* p) {
 
 // ---- bounded waiting --------------------------------------------------------------------
 // Every spin in this library goes through a SpinGuard: it gives up after `limit` clock
-// ticks (about two seconds at 2 GHz by default) or as soon as the kernel-wide abort word is
-// set, and reports which.
+// ticks (about two seconds by default) or as soon as the kernel-wide abort word is set, and
+// reports which.
 __device__ __forceinline__ long long clock_now() {
   long long t;
   asm volatile("mov.u64 %0, %%clock64;" : "=l"(t));
   return t;
 }
-// How long a wait may last, in SM clock ticks (set from the host when a context is created).
-__device__ long long g_spin_limit_cycles = 4000000000LL;
+// What every wait of a kernel shares: the kernel-wide abort word and how long a wait may last,
+// in SM clock ticks (a field of the launch parameters, so every context has its own limit).
+struct WaitCtx {
+  const volatile uint32_t* abort_word;
+  long long limit;
+};
 struct SpinGuard {
   long long start;
   uint32_t polls;
   __device__ __forceinline__ SpinGuard() : polls(0) { start = clock_now(); }
   // returns true when the caller must stop waiting
-  __device__ __forceinline__ bool expired(const volatile uint32_t* abort_word) {
+  __device__ __forceinline__ bool expired(const WaitCtx& w) {
     if ((++polls & 0x1F) != 0) return false;   // a poll may itself block for a while (try_wait)
-    if (abort_word != nullptr && *abort_word != 0) return true;
-    return (clock_now() - start) > g_spin_limit_cycles;
+    if (w.abort_word != nullptr && *w.abort_word != 0) return true;
+    return (clock_now() - start) > w.limit;
   }
 };
 
@@ -62,12 +66,11 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 // Bounded wait; false = gave up (timeout or abort).
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity,
-                                          const volatile uint32_t* abort_word) {
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const WaitCtx& w) {
   if (mbar_try_wait(bar, parity)) return true;
   SpinGuard g;
   while (!mbar_try_wait(bar, parity)) {
-    if (g.expired(abort_word)) return mbar_try_wait(bar, parity);
+    if (g.expired(w)) return mbar_try_wait(bar, parity);
   }
   return true;
 }
@@ -105,12 +108,11 @@ __device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t* bar, uint32_t pa
   return ok != 0;
 }
 // Bounded wait on a barrier that threads of the peer CTA (or its async units) arrive on.
-__device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity,
-                                                  const volatile uint32_t* abort_word) {
+__device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity, const WaitCtx& w) {
   if (mbar_try_wait_cluster(bar, parity)) return true;
   SpinGuard g;
   while (!mbar_try_wait_cluster(bar, parity)) {
-    if (g.expired(abort_word)) return mbar_try_wait_cluster(bar, parity);
+    if (g.expired(w)) return mbar_try_wait_cluster(bar, parity);
   }
   return true;
 }

@@ -506,6 +506,11 @@ extern "C" int fmoe_router_forward_static(const fmoe_model_desc* model, int32_t 
   if ((reinterpret_cast<uintptr_t>(a->tokens) | reinterpret_cast<uintptr_t>(a->weights) |
        reinterpret_cast<uintptr_t>(routes)) & 15)
     return set_error(FMOE_ERR_INVALID_ARG, "tokens, weights and routes must be 16-byte aligned");
+  if (reinterpret_cast<uintptr_t>(token_table) & 7)
+    return set_error(FMOE_ERR_INVALID_ARG, "token_table must be 8-byte aligned");
+  if ((reinterpret_cast<uintptr_t>(a->expert_counts) | reinterpret_cast<uintptr_t>(a->routing) |
+       reinterpret_cast<uintptr_t>(a->logit_bias)) & 3)
+    return set_error(FMOE_ERR_INVALID_ARG, "expert_counts, routing and logit_bias must be 4-byte aligned");
   if (round_ec < model->expert_peer_capacity)
     return set_error(FMOE_ERR_INVALID_ARG, "round_ec (row stride of token_table) is smaller than expert_peer_capacity");
   const long long pairs = static_cast<long long>(model->tokens_per_rank) * model->top_k;
@@ -518,8 +523,19 @@ extern "C" int fmoe_router_forward_static(const fmoe_model_desc* model, int32_t 
     return set_error(FMOE_ERR_UNSUPPORTED, "num_experts too large for the router's shared-memory rows");
   if (device_id < 0 || device_id >= kMaxDevices)
     return set_error(FMOE_ERR_INVALID_ARG, "device_id out of range");
-  cudaError_t ce = cudaSetDevice(device_id);
-  if (ce != cudaSuccess) return set_error(FMOE_ERR_CUDA, std::string("cudaSetDevice: ") + cudaGetErrorString(ce));
+  // The calling thread's current device is put back on every way out: a plug-in running between a
+  // host engine's own launches must not leave the engine on another GPU.
+  struct DeviceGuard {
+    int prev = -1;
+    ~DeviceGuard() { if (prev >= 0) cudaSetDevice(prev); }
+  } guard;
+  cudaError_t ce = cudaGetDevice(&guard.prev);
+  if (ce != cudaSuccess) { guard.prev = -1; return set_error(FMOE_ERR_CUDA, std::string("cudaGetDevice: ") + cudaGetErrorString(ce)); }
+  if (guard.prev == device_id) guard.prev = -1;   // nothing to restore
+  else {
+    ce = cudaSetDevice(device_id);
+    if (ce != cudaSuccess) return set_error(FMOE_ERR_CUDA, std::string("cudaSetDevice: ") + cudaGetErrorString(ce));
+  }
   void* scratch = nullptr;
   {
     // One-time set-up per device, with that device current: the array's name is only a host-side

@@ -151,17 +151,23 @@ class MoELayer:
     def phases(self) -> dict:
         """Per-phase times of the LAST forward from the kernel's per-CTA %globaltimer stamps, in
         microseconds: median over CTAs for each phase, the whole kernel (first start to last end),
-        and the share of the kernel a median CTA spent in communication it could not overlap
-        (count exchange + dispatch + waiting, after its own last task, for returned rows)."""
+        and the share of the kernel a median CTA spent in communication it could not overlap:
+        the count exchange, the wait of its first task for dispatched rows (tables built -> first
+        operand tiles landed) and the wait, after its own last task, for returned rows.  The
+        dispatch itself runs on the epilogue warps while the other warps are in the GEMM loop."""
         g = self.geometry()
-        t = self.debug(5, torch.int64, (g.grid, 8)).cpu().double()
-        d = (t[:, 1:] - t[:, :-1]) / 1e3
+        t = self.debug(5, torch.int64, (g.grid, 16)).cpu().double()
+        d = (t[:, 1:8] - t[:, 0:7]) / 1e3
         med = d.median(dim=0).values
+        first = t[:, 8] > 0                      # CTAs that issued MMAs at all
+        first_mma = float(((t[first, 8] - t[first, 2]) / 1e3).median()) if bool(first.any()) else 0.0
         out = {"count_exchange": float(med[0]), "tables": float(med[1]), "dispatch": float(med[2]),
-               "gemm_tickets": float(med[3]), "drain_last_task": float(med[4]),
+               "first_rows_wait": first_mma,
+               "gemm_tickets": float(((t[:, 4] - t[:, 2]) / 1e3).median()),
+               "drain_last_task": float(med[4]),
                "wait_returns": float(med[5]), "combine": float(med[6]),
                "kernel": float((t[:, 7].max() - t[:, 0].min()) / 1e3)}
-        out["exposed_comm_frac"] = (out["count_exchange"] + out["dispatch"] + out["wait_returns"]) / \
+        out["exposed_comm_frac"] = (out["count_exchange"] + out["first_rows_wait"] + out["wait_returns"]) / \
             max(out["kernel"], 1e-9)
         return out
 

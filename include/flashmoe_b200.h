@@ -106,7 +106,7 @@ enum {
   FMOE_PHASE_NONE = 0, FMOE_PHASE_COUNTS = 1, FMOE_PHASE_DISPATCH_ARRIVAL = 2,
   FMOE_PHASE_GEMM0_DONE = 3, FMOE_PHASE_RETURN_ARRIVAL = 4, FMOE_PHASE_PIPE_FULL = 5,
   FMOE_PHASE_PIPE_EMPTY = 6, FMOE_PHASE_TMEM_FULL = 7, FMOE_PHASE_TMEM_EMPTY = 8,
-  FMOE_PHASE_TASK = 9
+  FMOE_PHASE_TASK = 9, FMOE_PHASE_SPLIT_PARTS = 10
 };
 
 /* --- context life cycle -------------------------------------------------------------- */
@@ -156,6 +156,13 @@ int fmoe_ctx_destroy(fmoe_ctx* ctx, void* stream);
  * per layer, each with its own symmetric heap). */
 #define FMOE_LAYER_CACHE 128
 int fmoe_forward(fmoe_ctx* ctx, const fmoe_forward_args* args, void* stream);
+
+/* No counterpart in the reference (its FP32 kernels read fp32 weights directly).  An FP32 context
+ * runs the expert GEMMs on BF16 tensor cores with every weight held as three BF16 planes; it keeps
+ * the planes of the weight set it saw last, keyed by the three weight addresses, so the split is
+ * paid once per weight set and not per forward.  Call this after rewriting weights IN PLACE (same
+ * addresses); the next forward splits them again.  A no-op for BF16 / FP16 contexts. */
+int fmoe_weights_changed(fmoe_ctx* ctx);
 
 /* Replaces initializeGate / gate_initialize (bootstrap.cuh:413-447; bindings.py:238-264). */
 int fmoe_router_create(const fmoe_model_desc* model, int32_t device_id, int32_t return_logits,
@@ -207,7 +214,10 @@ int fmoe_forward_host_wait(fmoe_ctx* ctx, void* stream);
 
 /* --- diagnostics --------------------------------------------------------------------- */
 
-/* Reads the record the last forward left (synchronises `stream` first). */
+/* Reads the record the last forward left (synchronises `stream` first).  A record with a non-zero
+ * code marks the context as poisoned: from then on fmoe_forward and fmoe_router_forward on it
+ * return FMOE_ERR_DEVICE_TIMEOUT without launching; destroy it and create a new one (on every
+ * rank of the group). */
 int fmoe_last_status(fmoe_ctx* ctx, void* stream, fmoe_status* out);
 const char* fmoe_strerror(int code);
 /* Last host-side error message of the calling thread (empty string if none). */
@@ -223,7 +233,7 @@ typedef struct fmoe_geometry {
   int32_t grid, threads;   /* launch shape of the persistent kernel */
   int32_t smem_bytes;
   int32_t cta_pairs;       /* 1: tiles are worked by CTA pairs (cta_group::2), 0: by single CTAs */
-  int32_t reserved;
+  int32_t split_parts;     /* K parts per GEMM1 tile of the closing wave (1: no tile is cut) */
   int64_t symm_bytes, workspace_bytes;
 } fmoe_geometry;
 int fmoe_get_geometry(const fmoe_ctx* ctx, fmoe_geometry* out);
@@ -232,9 +242,11 @@ int fmoe_get_geometry(const fmoe_ctx* ctx, fmoe_geometry* out);
  * which: 0 landing rows [landing_rows, H], 1 landing meta [landing_rows] u32,
  *        2 GEMM0 output [landing_rows, I], 3 return rows [S*k, H],
  *        4 route records [S, k] of {int32 expert, int32 slot, float weight},
- *        5 phase stamps of the last forward: uint64 [grid][8] %globaltimer nanoseconds per CTA
- *          (0 start, 1 all ranks' counts in, 2 tables built, 3 dispatch done, 4 last ticket drawn,
- *           5 this CTA's last task finished, 6 all returns in, 7 combine done) */
+ *        5 phase stamps of the last forward: uint64 [grid][16] %globaltimer nanoseconds per CTA
+ *          (0 start, 1 all ranks' counts in, 2 tables built, 3 this CTA's share of the dispatch
+ *           done, 4 last ticket drawn, 5 this CTA's last task finished, 6 all returns in,
+ *           7 combine done, 8 first operand tiles of the CTA's first task landed (0: it had none),
+ *           9..15 unused) */
 int fmoe_debug_buffer(fmoe_ctx* ctx, int32_t which, void** ptr_out, size_t* bytes_out);
 
 #ifdef __cplusplus

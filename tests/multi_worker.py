@@ -18,7 +18,7 @@ sys.path.insert(0, HERE)
 sys.path.insert(0, os.path.dirname(HERE))
 
 from cases import GOLDEN_CASES  # noqa: E402
-from helpers import max_rel_err, oracle_layer  # noqa: E402
+from helpers import REL_TOL, elementwise_mismatch, max_rel_err, oracle_layer  # noqa: E402
 from flashmoe_b200.workloads import CONFIGS, make_tokens, make_weights  # noqa: E402
 
 
@@ -38,7 +38,7 @@ def main():
         w = w.scaled(tokens_per_rank=a.tokens)
     lw = make_weights(w)
     layer = MoELayer(w, lw, local)
-    worst = 0.0
+    worst, worst_frac = 0.0, 0.0
     ok = True
     try:
         for step in range(3):
@@ -46,12 +46,13 @@ def main():
             ref, _ = oracle_layer(w, x=x, lw=lw)
             out = layer.forward(x).cpu()
             err = max_rel_err(out, ref)
-            worst = max(worst, err)
-            ok = ok and bool(torch.isfinite(out.float()).all()) and err <= 2e-2
+            frac, _ = elementwise_mismatch(out, ref, w.data_type)
+            worst, worst_frac = max(worst, err), max(worst_frac, frac)
+            ok = ok and bool(torch.isfinite(out.float()).all()) and err <= REL_TOL[int(w.data_type)] and frac == 0.0
     finally:
         layer.close()
     res = [None] * world
-    dist.all_gather_object(res, {"rank": rank, "ok": ok, "err": worst})
+    dist.all_gather_object(res, {"rank": rank, "ok": ok, "err": worst, "mismatch_frac": worst_frac})
     if rank == 0:
         print("MULTI_RESULT " + json.dumps(res))
     dist.destroy_process_group()

@@ -59,10 +59,16 @@ def test_static_router_matches_the_context_router_twice_in_a_row():
             args = N.RouterArgsC(layer.tokens.data_ptr(), layer.router_w.data_ptr(), probs.data_ptr(),
                                  counts.data_ptr(),
                                  layer.logit_bias.data_ptr() if layer.logit_bias is not None else None)
+            # the one property this entry point exists for: the device's free memory is the same
+            # before and after (the first call only looks up the address of the library's array)
+            torch.cuda.synchronize()
+            free_before, _ = torch.cuda.mem_get_info()
             rc = lib.fmoe_router_forward_static(C.byref(desc), 0, C.byref(args), C.c_void_p(table.data_ptr()),
                                                 g.round_ec, C.c_void_p(routes.data_ptr()), C.c_void_p(sp))
             assert rc == 0, lib.fmoe_last_error().decode()
             layer.stream.synchronize()
+            free_after, _ = torch.cuda.mem_get_info()
+            assert free_after == free_before, f"call {call}: {free_before - free_after} bytes of device memory taken"
             # integer and bit-level equality (the tolerance of every router test in this suite)
             assert torch.equal(counts, want_counts), f"call {call}: counts"
             assert torch.equal(probs.view(torch.int32), want_probs.view(torch.int32)), f"call {call}: probs"
@@ -76,6 +82,33 @@ def test_static_router_matches_the_context_router_twice_in_a_row():
                 assert np.array_equal(gt[e, :n], wt[e, :n]), f"call {call}: table row {e}"
     finally:
         layer.close()
+
+
+def test_static_router_checks_alignment_and_leaves_the_current_device_alone():
+    """An offset pointer is refused on the host (a misaligned store would fault the GPU), and the
+    calling thread's current device is what it was, also when the call names another device."""
+    lib = N.lib()
+    desc = N.ModelDesc(64, 64, 64, 8, 2, 64, 0, 0, 1, 1000)
+    buf = torch.zeros(4096, dtype=torch.int32, device="cuda")
+    base = buf.data_ptr()
+    ok = N.RouterArgsC(base, base, None, base, None)
+    assert lib.fmoe_router_forward_static(C.byref(desc), 0, C.byref(ok), C.c_void_p(base + 4), 128,
+                                          C.c_void_p(base), None) == 1
+    assert b"token_table" in lib.fmoe_last_error()
+    odd = N.RouterArgsC(base, base, None, base + 2, None)
+    assert lib.fmoe_router_forward_static(C.byref(desc), 0, C.byref(odd), C.c_void_p(base), 128,
+                                          C.c_void_p(base), None) == 1
+    if torch.cuda.device_count() > 1:
+        # tokens on device 1, the caller's thread on device 0
+        with torch.cuda.device(1):
+            far = torch.zeros(1 << 16, dtype=torch.int32, device="cuda")
+        torch.cuda.set_device(0)
+        p1 = far.data_ptr()
+        a1 = N.RouterArgsC(p1, p1 + 8192, None, p1 + 16384, None)
+        assert lib.fmoe_router_forward_static(C.byref(desc), 1, C.byref(a1), C.c_void_p(p1 + 32768), 128,
+                                              C.c_void_p(p1 + 65536), None) == 0, lib.fmoe_last_error().decode()
+        torch.cuda.synchronize(1)
+        assert torch.cuda.current_device() == 0
 
 
 def test_static_router_rejects_oversized_layers():
