@@ -51,7 +51,8 @@ class _MoEModule:
         if ep_world > 1:
             handle = (C.c_ubyte * N.IPC_HANDLE_BYTES)()
             N.check(self._lib.fmoe_symm_export(ctx, handle), "initialize (export)")
-            for peer, blob in enumerate(cb.all_gather_bytes(bytes(handle))):
+            # peers are addressed by EP rank; rank_map says which process of the job each one is
+            for peer, blob in enumerate(cb.exchange_by_rank_map(bytes(handle), ep_rank, list(rank_map))):
                 if peer != ep_rank:
                     buf = (C.c_ubyte * N.IPC_HANDLE_BYTES).from_buffer_copy(blob)
                     N.check(self._lib.fmoe_symm_import(ctx, peer, buf), "initialize (import)")

@@ -72,6 +72,32 @@ def all_gather_bytes(payload: bytes) -> List[bytes]:
     return out
 
 
+def exchange_by_rank_map(payload: bytes, ep_rank: int, rank_map) -> List[bytes]:
+    """Every process hands in `payload` and its expert-parallel rank; returns the payloads of this
+    process's EP group ordered by EP rank.  `rank_map[p]` is the global rank (position in the
+    default process group) of EP rank p, as in the reference (bootstrap.cuh:140,
+    epRankToGlobalRank): the map may be a permutation of the world, and an EP group may be a
+    subset of it (every process of the world still takes part in the gather).  Raises ValueError
+    when the map does not describe this process or when the peers disagree with it."""
+    mine = get_rank()
+    ep_world = len(rank_map)
+    if not 0 <= ep_rank < ep_world or rank_map[ep_rank] != mine:
+        raise ValueError(f"rank_map[{ep_rank}] = {rank_map[ep_rank] if 0 <= ep_rank < ep_world else '?'} "
+                         f"but this process is global rank {mine}")
+    if len(set(rank_map)) != ep_world or min(rank_map) < 0 or max(rank_map) >= get_world_size():
+        raise ValueError("rank_map must name ep_world distinct global ranks of this job")
+    tagged = all_gather_bytes(ep_rank.to_bytes(4, "little") + payload)
+    out = []
+    for p in range(ep_world):
+        blob = tagged[rank_map[p]]
+        theirs = int.from_bytes(blob[:4], "little")
+        if theirs != p:
+            raise ValueError(f"rank_map says global rank {rank_map[p]} is EP rank {p}, "
+                             f"but that process says it is EP rank {theirs}")
+        out.append(blob[4:])
+    return out
+
+
 def sync_all(stream_ptr: int) -> None:
     """Drain `stream_ptr`, then barrier across ranks (cb.py:67-72: nvshmem sync_all)."""
     assert IS_INITIALIZED

@@ -173,7 +173,7 @@ struct Plan {
 
 // GEMM1 tiles of the closing wave are cut along K into this many tickets (FMOE_SPLIT_PARTS
 // overrides; 1 = never).  The count of cut tiles is one wave of the largest grid (one CTA per SM).
-constexpr int kSplitPartsDefault = 4;
+constexpr int kSplitPartsDefault = 2;
 constexpr int kSplitTilesMax = 160;
 
 int split_parts_for(const fmoe_model_desc& m) {
@@ -213,7 +213,7 @@ Plan plan_sizes(const fmoe_model_desc& m, int W, int nLx) {
   pl.w_y = w; w = align_up(w + static_cast<size_t>(planes) * pl.landing_rows * I * 2, 1024);
   pl.split_parts = split_parts_for(m);
   pl.split_tiles = pl.split_parts > 1 ? kSplitTilesMax : 0;
-  pl.w_split = w; w = align_up(w + static_cast<size_t>(pl.split_tiles) * (pl.split_parts - 1) * kTileM * kUmmaN * sizeof(float), 1024);
+  pl.w_split = w; w = align_up(w + static_cast<size_t>(pl.split_tiles) * pl.split_parts * kTileM * kUmmaN * sizeof(float), 1024);
   pl.w_done = w; w = align_up(w + sizeof(uint32_t) * pl.max_mtiles, 256);
   pl.w_split_done = w; w = align_up(w + sizeof(uint32_t) * 4 * (pl.split_tiles + 1), 256);
   pl.w_ctl = w; w = align_up(w + 256, 256);   // ticket, done_ctas, abort, epoch

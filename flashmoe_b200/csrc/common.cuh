@@ -75,7 +75,7 @@ struct MoeParams {
   // private workspace
   void* y;                 // Element [landing_rows][I]  GEMM0 output
   uint32_t* gemm0_done;    // [max_mtiles] finished N0 tiles per M tile
-  float* split_scratch;    // [split_tiles][split_parts - 1][128 x 256] fp32 partial sums of the cut tiles
+  float* split_scratch;    // [split_tiles][split_parts][128 x 256] fp32 partial sums of the cut tiles
   uint32_t* split_done;    // [split_tiles][4] parts parked, per tile and epilogue warp
   uint32_t* ticket;        // next task
   uint32_t* done_ctas;

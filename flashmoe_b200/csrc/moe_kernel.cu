@@ -242,11 +242,14 @@ struct Tables {
   int* seg_whole;  // [2 nLx] GEMM1 segments: leading tickets that cover a whole tile (the rest are K parts)
   int* tot;        // [E]    rows expert e receives from all sources
   int* tmp;        // [E]    scratch of the table construction
+  int* owner;      // [E]    expert -> rank                      (copies of the context's maps, so
+  int* lidx;       // [E]    expert -> index at its owner         that nothing after the count
+  int* local_e;    // [W][nLx] -> expert                          exchange waits on global memory)
 };
 
 __host__ __device__ inline size_t tables_ints(int W, int E, int nLx) {
   return static_cast<size_t>(W) * E + E + E + (E + 1) + nLx + nLx + (nLx + 1) + (2 * nLx + 1) +
-         2 * nLx + 2 * nLx + 2 * nLx + E + E;
+         2 * nLx + 2 * nLx + 2 * nLx + E + E + E + E + static_cast<size_t>(W) * nLx;
 }
 
 // kPair = true: CTA pairs on 256-row tile groups (experts with several M tiles; tensor-bound work).
@@ -281,7 +284,10 @@ __device__ __forceinline__ void moe_forward_body(const MoeParams& p, const TmaMa
     tb.seg_lx = q; q += 2 * p.nLx;
     tb.seg_whole = q; q += 2 * p.nLx;
     tb.tot = q; q += p.E;
-    tb.tmp = q;
+    tb.tmp = q; q += p.E;
+    tb.owner = q; q += p.E;
+    tb.lidx = q; q += p.E;
+    tb.local_e = q;
   }
   const WaitCtx wc{p.abort_word, p.spin_limit};
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -353,23 +359,105 @@ __device__ __forceinline__ void moe_forward_body(const MoeParams& p, const TmaMa
       int32_t* t = reinterpret_cast<int32_t*>(p.peers[r] + p.lay.cnt_table);
       t[(static_cast<size_t>(parity) * W + p.rank) * E + e] = p.expert_counts[e];
     }
-    __threadfence_system();
+    // the barrier orders every thread's writes above before the releases below; one release per
+    // peer is the only system-wide fence of the exchange (device-wide with a single rank)
     __syncthreads();
     // (a context created with FMOE_WITHHOLD_FLAGS=1 never publishes the flags: every CTA's wait
     // below then runs out, which is how the tests exercise the bounded-wait and status path
     // without faulting anything)
     if (tid < W && !p.withhold_flags) {
-      uint64_t* f = reinterpret_cast<uint64_t*>(p.peers[tid] + p.lay.cnt_flag);
-      fence_acq_rel_sys();
-      st_release_sys(f + parity * W + p.rank, flag_val);
+      uint64_t* f = reinterpret_cast<uint64_t*>(p.peers[tid] + p.lay.cnt_flag) + parity * W + p.rank;
+      if (W > 1) st_release_sys(f, flag_val); else st_release_gpu(f, flag_val);
     }
   }
+  // ---- what depends on this rank's own counts only, while the other ranks' counts travel ----
+  // exclusive prefix sums by one warp, 32 entries per step: emit(i, sum of values before i)
+  auto warp_scan = [&](auto value_of, auto emit, int n) -> int {   // returns the total
+    int carry = 0;
+    for (int base = 0; base < n; base += 32) {
+      const int i = base + lane;
+      const int v = i < n ? value_of(i) : 0;
+      int incl = v;
+#pragma unroll
+      for (int off = 1; off < 32; off <<= 1) {
+        const int u = __shfl_up_sync(0xffffffffu, incl, off);
+        if (lane >= off) incl += u;
+      }
+      if (i < n) emit(i, carry + incl - v);
+      carry += __shfl_sync(0xffffffffu, incl, 31);
+    }
+    return carry;
+  };
+  // Send order: the experts that are in the first half of their owner's local list come first
+  // (class 0), the others after them (class 1); inside a class ascending expert id.  Every warp
+  // sends its share of class 0 before its share of class 1, so the rows the owners' first GEMM0
+  // tickets wait for are on the wire first and the second half of the transfer overlaps compute.
+  for (int e = tid; e < E; e += kThreads) {
+    tb.owner[e] = p.owner[e]; tb.lidx[e] = p.lidx[e]; tb.local_e[e] = p.local_e[e];   // W * nLx == E
+  }
+  __syncthreads();
+  auto first_class = [&](int e) { return 2 * tb.lidx[e] < nLx ? 1 : 0; };
+  if (warp == 0) {
+    const int e0 = warp_scan(first_class, [&](int e, int v) { tb.tmp[e] = v; }, E);
+    __syncwarp();
+    for (int e = lane; e < E; e += 32) {
+      const int before = tb.tmp[e];
+      tb.ord[first_class(e) ? before : e0 + (e - before)] = e;
+    }
+    __syncwarp();
+    const int sp = warp_scan([&](int i) { const int v = p.expert_counts[tb.ord[i]]; return v < p.EC ? (v < 0 ? 0 : v) : p.EC; },
+                             [&](int i, int v) { tb.send_pref[i] = v; }, E);
+    if (lane == 0) {
+      tb.send_pref[E] = sp;
+      ctl->send_rows = sp;
+      ctl->class0_experts = e0;
+      ctl->expected_ret = sp * p.tiles_n1;   // one count per returned row and N1 tile
+    }
+  }
+  __syncthreads();
+  // One routed row: where it stands in the send order, which token it is and which of the token's
+  // k choices.  Lane i of a dispatching warp looks up row (q + i): the dependent loads (routing
+  // table, then the token's route records) are in flight before the counts of the peers are in.
+  struct RowInfo { int pos, row; uint32_t token, choice; };
+  // This warp's share of the rows to send (epilogue warps): its slice of class 0 followed by its
+  // slice of class 1, as one list; entry v of the list is row a0 + v, or a1 + (v - n0).
+  int a0 = 0, n0 = 0, a1 = 0, n1 = 0;
+  auto lookup = [&](int v0) -> RowInfo {      // lane i looks up list entry v0 + i
+    RowInfo ri{0, 0, 0u, 0u};
+    const int v = v0 + lane;
+    if (v < n0 + n1) {
+      const int row = v < n0 ? a0 + v : a1 + (v - n0);
+      int lo = 0, hi = E;  // largest position with send_pref[position] <= row
+      while (hi - lo > 1) {
+        const int mid = (lo + hi) >> 1;
+        if (tb.send_pref[mid] <= row) lo = mid; else hi = mid;
+      }
+      const int e = tb.ord[lo];
+      ri.pos = lo;
+      ri.row = row;
+      ri.token = p.table[static_cast<size_t>(e) * p.round_ec + (row - tb.send_pref[lo])].token;
+      for (int c = 0; c < p.k; ++c)
+        if (p.routes[static_cast<size_t>(ri.token) * p.k + c].expert == e) { ri.choice = c; break; }
+    }
+    return ri;
+  };
+  RowInfo pre{0, 0, 0u, 0u};
+  if (warp >= 2) {
+    const int G = gridDim.x * 4;
+    const int gw = blockIdx.x * 4 + (warp - 2);
+    const long long R0 = tb.send_pref[ctl->class0_experts], R1 = ctl->send_rows - R0;
+    a0 = static_cast<int>(R0 * gw / G); n0 = static_cast<int>(R0 * (gw + 1) / G) - a0;
+    a1 = static_cast<int>(R0 + R1 * gw / G); n1 = static_cast<int>(R0 + R1 * (gw + 1) / G) - a1;
+    pre = lookup(0);
+  }
+
   if (tid < W) {
     const uint64_t* f = reinterpret_cast<const uint64_t*>(self + p.lay.cnt_flag) + parity * W + tid;
+    auto poll = [&]() { return W > 1 ? ld_acquire_sys(f) : ld_acquire_gpu(f); };
     SpinGuard g;
     bool ok = true;
-    while (ld_acquire_sys(f) != flag_val) {
-      if (g.expired(wc)) { ok = (ld_acquire_sys(f) == flag_val); break; }
+    while (poll() != flag_val) {
+      if (g.expired(wc)) { ok = (poll() == flag_val); break; }
     }
     if (!ok) { fail(p, FMOE_PHASE_COUNTS, tid); ctl->ok = 0; }
   }
@@ -397,59 +485,24 @@ __device__ __forceinline__ void moe_forward_body(const MoeParams& p, const TmaMa
     }
   }
   __syncthreads();
-  // exclusive prefix sums by one warp, 32 entries per step: emit(i, sum of values before i)
-  auto warp_scan = [&](auto value_of, auto emit, int n) -> int {   // returns the total
-    int carry = 0;
-    for (int base = 0; base < n; base += 32) {
-      const int i = base + lane;
-      const int v = i < n ? value_of(i) : 0;
-      int incl = v;
-#pragma unroll
-      for (int off = 1; off < 32; off <<= 1) {
-        const int u = __shfl_up_sync(0xffffffffu, incl, off);
-        if (lane >= off) incl += u;
-      }
-      if (i < n) emit(i, carry + incl - v);
-      carry += __shfl_sync(0xffffffffu, incl, 31);
-    }
-    return carry;
-  };
   if (ctl->ok) {
     // landing-row base of every expert at its owner: that owner's experts in local order, each
     // rounded up to whole M tiles (one warp per owner rank)
     for (int r = warp; r < W; r += kThreads / 32) {
-      warp_scan([&](int lx) { return (tb.tot[p.local_e[r * nLx + lx]] + kTileM - 1) / kTileM * kTileM; },
+      warp_scan([&](int lx) { return (tb.tot[tb.local_e[r * nLx + lx]] + kTileM - 1) / kTileM * kTileM; },
                 [&](int lx, int base) {
-                  const int e = p.local_e[r * nLx + lx];
+                  const int e = tb.local_e[r * nLx + lx];
                   tb.dst_row0[e] += base;
                   if (r == p.rank) { tb.lx_base[lx] = base; tb.lx_rows[lx] = tb.tot[e]; }
                 }, nLx);
     }
   }
   __syncthreads();
-  // Send order: the experts that are in the first half of their owner's local list come first
-  // (class 0), the others after them (class 1); inside a class ascending expert id.  Every warp
-  // sends its share of class 0 before its share of class 1, so the rows the owners' first GEMM0
-  // tickets wait for are on the wire first and the second half of the transfer overlaps compute.
-  auto first_class = [&](int e) { return 2 * p.lidx[e] < nLx ? 1 : 0; };
   if (ctl->ok && warp == 0) {
-    const int e0 = warp_scan(first_class, [&](int e, int v) { tb.tmp[e] = v; }, E);
-    __syncwarp();
-    for (int e = lane; e < E; e += 32) {
-      const int before = tb.tmp[e];
-      tb.ord[first_class(e) ? before : e0 + (e - before)] = e;
-    }
-    __syncwarp();
-    const int sp = warp_scan([&](int i) { return tb.n[p.rank * E + tb.ord[i]]; },
-                             [&](int i, int v) { tb.send_pref[i] = v; }, E);
     const int mt = warp_scan([&](int lx) { return (tb.lx_rows[lx] + kTileM - 1) / kTileM; },
                              [&](int lx, int v) { tb.lx_mt0[lx] = v; }, nLx);
     if (lane == 0) {
-      tb.send_pref[E] = sp;
       tb.lx_mt0[nLx] = mt;
-      ctl->send_rows = sp;
-      ctl->class0_experts = e0;
-      ctl->expected_ret = sp * p.tiles_n1;   // one count per returned row and N1 tile
       ctl->lag = nLx;
     }
   }
@@ -503,78 +556,70 @@ __device__ __forceinline__ void moe_forward_body(const MoeParams& p, const TmaMa
   // 1 are already drawing tickets and loading weights.  A GEMM0 ticket waits for the rows of its
   // own M tile only (per source, on disp_arrived) and the dispatch depends on no ticket, so the
   // order stays deadlock-free; the first epilogue is due one whole main loop after the first MMA.
-  auto dispatch_range = [&](int q, const int q_end) {
+  auto send_rows = [&](const int v0, const RowInfo ri) {   // list entries v0 .. v0 + 31
     const int vecs = p.H * EB / 16;
     const uint4* tok_base = static_cast<const uint4*>(p.tokens);
-    while (q < q_end) {
-      int lo = 0, hi = E;  // largest position with send_pref[position] <= q
-      while (hi - lo > 1) {
-        const int mid = (lo + hi) >> 1;
-        if (tb.send_pref[mid] <= q) lo = mid; else hi = mid;
-      }
-      const int e = tb.ord[lo];
-      const int first = tb.send_pref[lo];
-      const int run_end = min(q_end, tb.send_pref[lo + 1]);
-      const int r = p.owner[e], lx = p.lidx[e];
-      char* peer = p.peers[r];
-      const int run_start = q;
-      while (q < run_end) {
-        // up to 32 rows at a time: lane i fetches row (q + i)'s token id and which of the token's
-        // k choices this expert is, so that the copies below do not wait on those look-ups
-        const int batch = min(32, run_end - q);
-        uint32_t my_token = 0, my_choice = 0;
-        if (lane < batch) {
-          my_token = p.table[static_cast<size_t>(e) * p.round_ec + (q - first) + lane].token;
-          for (int c = 0; c < p.k; ++c)
-            if (p.routes[static_cast<size_t>(my_token) * p.k + c].expert == e) { my_choice = c; break; }
+    const int n = min(32, n0 + n1 - v0);
+    for (int i = 0; i < n; ++i) {
+      const int pos = __shfl_sync(0xffffffffu, ri.pos, i);
+      const int row = __shfl_sync(0xffffffffu, ri.row, i);
+      const uint32_t token = __shfl_sync(0xffffffffu, ri.token, i);
+      const uint32_t choice = __shfl_sync(0xffffffffu, ri.choice, i);
+      const int e = tb.ord[pos];
+      char* peer = p.peers[tb.owner[e]];
+      const int drow = tb.dst_row0[e] + (row - tb.send_pref[pos]);
+      const uint4* src = tok_base + static_cast<size_t>(token) * vecs;
+      if constexpr (kPlanes == 1) {
+        uint4* dst = reinterpret_cast<uint4*>(peer + p.lay.landing) + static_cast<size_t>(drow) * vecs;
+        // A warp owns only a row or two, so its time is a chain of load -> store round trips:
+        // twenty 16-byte loads in flight per lane make a 5120-element row one trip instead of five.
+        constexpr int kDepth = 20;
+        for (int w0 = lane; w0 < vecs; w0 += 32 * kDepth) {
+          uint4 x[kDepth];
+#pragma unroll
+          for (int u = 0; u < kDepth; ++u) if (w0 + 32 * u < vecs) x[u] = __ldg(src + w0 + 32 * u);
+#pragma unroll
+          for (int u = 0; u < kDepth; ++u) if (w0 + 32 * u < vecs) dst[w0 + 32 * u] = x[u];
         }
-        for (int i = 0; i < batch; ++i) {
-          const uint32_t token = __shfl_sync(0xffffffffu, my_token, i);
-          const uint32_t choice = __shfl_sync(0xffffffffu, my_choice, i);
-          const int drow = tb.dst_row0[e] + (q - first) + i;
-          const uint4* src = tok_base + static_cast<size_t>(token) * vecs;
-          if constexpr (kPlanes == 1) {
-            uint4* dst = reinterpret_cast<uint4*>(peer + p.lay.landing) + static_cast<size_t>(drow) * vecs;
-            // A warp owns only a row or two, so its time is a chain of load -> store round trips:
-            // ten 16-byte loads in flight per lane make a 5120-element row two trips instead of five.
-            constexpr int kDepth = 10;
-            for (int v0 = lane; v0 < vecs; v0 += 32 * kDepth) {
-              uint4 x[kDepth];
+      } else {
+        // fp32 row -> three BF16 planes at the owner (4 floats in, 3 x 8 bytes out)
+        for (int w = lane; w < vecs; w += 32) {
+          const uint4 raw = __ldg(src + w);
+          const float f[4] = {__uint_as_float(raw.x), __uint_as_float(raw.y), __uint_as_float(raw.z),
+                              __uint_as_float(raw.w)};
+          unsigned short h[4][3];
 #pragma unroll
-              for (int u = 0; u < kDepth; ++u) if (v0 + 32 * u < vecs) x[u] = __ldg(src + v0 + 32 * u);
+          for (int z = 0; z < 4; ++z) split3(f[z], h[z]);
 #pragma unroll
-              for (int u = 0; u < kDepth; ++u) if (v0 + 32 * u < vecs) dst[v0 + 32 * u] = x[u];
-            }
-          } else {
-            // fp32 row -> three BF16 planes at the owner (4 floats in, 3 x 8 bytes out)
-            for (int v = lane; v < vecs; v += 32) {
-              const uint4 raw = __ldg(src + v);
-              const float f[4] = {__uint_as_float(raw.x), __uint_as_float(raw.y), __uint_as_float(raw.z),
-                                  __uint_as_float(raw.w)};
-              unsigned short h[4][3];
-#pragma unroll
-              for (int z = 0; z < 4; ++z) split3(f[z], h[z]);
-#pragma unroll
-              for (int pl = 0; pl < 3; ++pl) {
-                uint2* dst = reinterpret_cast<uint2*>(peer + p.lay.landing + pl * landing_plane) +
-                             static_cast<size_t>(drow) * vecs + v;
-                *dst = make_uint2(static_cast<uint32_t>(h[0][pl]) | (static_cast<uint32_t>(h[1][pl]) << 16),
-                                  static_cast<uint32_t>(h[2][pl]) | (static_cast<uint32_t>(h[3][pl]) << 16));
-              }
-            }
+          for (int pl = 0; pl < 3; ++pl) {
+            uint2* dst = reinterpret_cast<uint2*>(peer + p.lay.landing + pl * landing_plane) +
+                         static_cast<size_t>(drow) * vecs + w;
+            *dst = make_uint2(static_cast<uint32_t>(h[0][pl]) | (static_cast<uint32_t>(h[1][pl]) << 16),
+                              static_cast<uint32_t>(h[2][pl]) | (static_cast<uint32_t>(h[3][pl]) << 16));
           }
-          if (lane == 0)
-            reinterpret_cast<uint32_t*>(peer + p.lay.landing_meta)[drow] =
-                (static_cast<uint32_t>(p.rank) << kMetaSrcShift) | (token * p.k + choice);
         }
-        q += batch;
       }
-      const int sent = run_end - run_start;
-      // every lane's stores happen before the barrier, the barrier before lane 0's release
-      __syncwarp();
-      if (lane == 0 && sent > 0)
-        red_add_release_sys(reinterpret_cast<uint32_t*>(peer + p.lay.disp_arrived) + p.rank * nLx + lx,
-                            static_cast<uint32_t>(sent));
+      if (lane == 0)
+        reinterpret_cast<uint32_t*>(peer + p.lay.landing_meta)[drow] =
+            (static_cast<uint32_t>(p.rank) << kMetaSrcShift) | (token * p.k + choice);
+    }
+    // Count the rows in at their owners, one update per expert.  Every lane's stores happen before
+    // the barrier, the barrier before lane 0's fence, and that ONE fence orders them before all the
+    // updates lane 0 makes after it (a fence per update would cost a trip over the link each).
+    __syncwarp();
+    if (lane == 0) { if (W > 1) fence_acq_rel_sys(); else fence_acq_rel_gpu(); }
+    const int prev = __shfl_up_sync(0xffffffffu, ri.pos, 1);
+    unsigned heads = __ballot_sync(0xffffffffu, lane < n && (lane == 0 || prev != ri.pos));
+    while (heads != 0) {
+      const int h = __ffs(heads) - 1;
+      heads &= heads - 1;
+      const int end = heads != 0 ? __ffs(heads) - 1 : n;      // the next run's first entry
+      const int pos = __shfl_sync(0xffffffffu, ri.pos, h);
+      if (lane == 0) {
+        const int e = tb.ord[pos];
+        red_add_relaxed_sys(reinterpret_cast<uint32_t*>(p.peers[tb.owner[e]] + p.lay.disp_arrived) + p.rank * nLx + tb.lidx[e],
+                            static_cast<uint32_t>(end - h));
+      }
     }
   };
 
@@ -648,14 +693,16 @@ __device__ __forceinline__ void moe_forward_body(const MoeParams& p, const TmaMa
         if (leader) {
           // readiness of BOTH M tiles of the group, then hand the ticket to the follower
           if (t.kind == kTaskGemm0) {
-            const int e = p.local_e[p.rank * nLx + t.lx];
+            const int e = tb.local_e[p.rank * nLx + t.lx];
             const uint32_t* arrived = reinterpret_cast<const uint32_t*>(self + p.lay.disp_arrived);
             const int lo_row = t.m_in_expert * kTileM, hi_row = lo_row + kGroup * kTileM;
             int off = 0;
             for (int s = 0; s < W && ok; ++s) {
               const int ns = tb.n[s * E + e];
               if (ns > 0 && off < hi_row && off + ns > lo_row) {
-                if (!wait_counter_sys(arrived + s * nLx + t.lx, static_cast<uint32_t>(ns), wc)) {
+                const bool in = W > 1 ? wait_counter_sys(arrived + s * nLx + t.lx, static_cast<uint32_t>(ns), wc)
+                                      : wait_counter_gpu(arrived + s * nLx + t.lx, static_cast<uint32_t>(ns), wc);
+                if (!in) {
                   fail(p, FMOE_PHASE_DISPATCH_ARRIVAL, s); ok = false;
                 }
               }
@@ -797,18 +844,8 @@ __device__ __forceinline__ void moe_forward_body(const MoeParams& p, const TmaMa
       }
     }
   } else if (ctl->ok) {
-    {
-      // this warp's share of the rows to send: its slice of class 0, then its slice of class 1
-      const int G = gridDim.x * 4;
-      const int gw = blockIdx.x * 4 + (warp - 2);
-      const long long R0 = tb.send_pref[ctl->class0_experts], R1 = ctl->send_rows - R0;
-#pragma unroll 1
-      for (int c = 0; c < 2; ++c) {
-        const long long base = c ? R0 : 0, n = c ? R1 : R0;
-        dispatch_range(static_cast<int>(base + n * gw / G), static_cast<int>(base + n * (gw + 1) / G));
-      }
-      if (warp == 2 && lane == 0) stamp_now(3);
-    }
+    for (int v0 = 0; v0 < n0 + n1; v0 += 32) send_rows(v0, v0 == 0 ? pre : lookup(v0));
+    if (warp == 2 && lane == 0) stamp_now(3);
     // epilogue warps: TMEM lane quadrant = warp id mod 4; this CTA's 128 rows of the pair's tile
     const int quad = warp & 3;
     const int row_in_tile = quad * 32 + lane;
@@ -828,6 +865,7 @@ __device__ __forceinline__ void moe_forward_body(const MoeParams& p, const TmaMa
         fail(p, FMOE_PHASE_TMEM_FULL, t.mt); break;
       }
       tc_fence_after_sync();
+      if (warp == 2 && lane == 0) stamp_now(9);
       const uint32_t taddr = ctl->tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + buf * kUmmaN;
       const bool valid = row_in_tile < t.rows;
       const int row = t.row0 + row_in_tile;
@@ -910,100 +948,132 @@ __device__ __forceinline__ void moe_forward_body(const MoeParams& p, const TmaMa
         // every lane's stores happen before the barrier, the barrier before lane 0's release
         __syncwarp();
         if (lane == 0 && t.rows > 0) red_add_release_gpu(p.gemm0_done + t.mt, 1u);
-      } else if (t.nparts > 1 && t.part < t.nparts - 1) {
-        // One K part of a tile of the closing wave, not the last: park the fp32 partial sums (chunk
-        // c, column i, row r at [(32 c + i) * 128 + r], so that a warp writes whole lines) and
-        // count this warp's quarter in.
-        float* part = p.split_scratch +
-                      (static_cast<size_t>(t.split_idx) * (p.split_parts - 1) + t.part) * (kTileM * kUmmaN);
-#pragma unroll 1
-        for (int c = 0; c < kUmmaN / 32; ++c) {
-          uint32_t a[32];
-          __syncwarp();
-          tmem_ld_32x32(taddr + c * 32, a);
-          tmem_ld_wait();
-          if constexpr (kPlanes == 3) {
-            uint32_t ca[32];
-            tmem_ld_32x32(taddr + kUmmaN + c * 32, ca);
-            tmem_ld_wait();
-#pragma unroll
-            for (int i = 0; i < 32; ++i) a[i] = __float_as_uint(__uint_as_float(a[i]) + __uint_as_float(ca[i]));
-          }
-          if (c == kUmmaN / 32 - 1) release_acc();
-#pragma unroll
-          for (int i = 0; i < 32; ++i) __stcg(part + (c * 32 + i) * kTileM + row_in_tile, __uint_as_float(a[i]));
-        }
-        // every lane's stores happen before the barrier, the barrier before lane 0's release
-        __syncwarp();
-        if (lane == 0) red_add_release_gpu(p.split_done + t.split_idx * 4 + quad, 1u);
       } else {
-        uint32_t meta = 0;
-        if (valid) meta = __ldcg(reinterpret_cast<const uint32_t*>(self + p.lay.landing_meta) + row);
-        const int src = static_cast<int>(meta >> kMetaSrcShift);
-        const uint32_t ret_row = meta & ((1u << kMetaSrcShift) - 1);
-        char* orow = p.peers[valid ? src : p.rank] + p.lay.ret + static_cast<size_t>(ret_row) * p.H * EB;
-        const int col_base = t.n * kUmmaN;
-        // The last K part of a split tile adds the parked partial sums of the parts before it, in
-        // part order, and finishes the tile.  Those parts hold smaller tickets, so waiting for them
-        // here keeps the task order deadlock-free; they were drawn at about the same time.
-        const float* parts = nullptr;
-        if (t.nparts > 1) {
-          parts = p.split_scratch + static_cast<size_t>(t.split_idx) * (p.split_parts - 1) * (kTileM * kUmmaN);
-          bool ready = true;
-          if (lane == 0)
-            ready = wait_counter_gpu(p.split_done + t.split_idx * 4 + quad, static_cast<uint32_t>(t.nparts - 1), wc);
-          ready = __shfl_sync(0xffffffffu, ready ? 1 : 0, 0) != 0;
-          if (!ready) { if (lane == 0) fail(p, FMOE_PHASE_SPLIT_PARTS, t.mt); break; }
-        }
+        // GEMM1.  A tile of the closing wave arrives as `nparts` tickets, one per K range: every
+        // part parks its fp32 partial sums (column quad j of chunk c, row r at float4 index
+        // (8 c + j) * 128 + r, so that a warp moves whole 512-byte lines) and counts itself in; the
+        // part that counts in last adds all of them up in part order, whichever it is, and
+        // finishes the tile.  Nobody waits for anybody, and the sum does not depend on who was last.
+        const bool split = t.nparts > 1;
+        constexpr int kTileFloats = kTileM * kUmmaN;
+        bool finish = true;
+        if (split) {
+          float4* mine = reinterpret_cast<float4*>(
+                             p.split_scratch + (static_cast<size_t>(t.split_idx) * p.split_parts + t.part) * kTileFloats) +
+                         row_in_tile;
 #pragma unroll 1
-        for (int c = 0; c < kUmmaN / 32; ++c) {
-          uint32_t a[32];
-          __syncwarp();
-          tmem_ld_32x32(taddr + c * 32, a);
-          tmem_ld_wait();
-          if constexpr (kPlanes == 3) {
-            uint32_t ca[32];
-            tmem_ld_32x32(taddr + kUmmaN + c * 32, ca);
+          for (int c = 0; c < kUmmaN / 32; ++c) {
+            uint32_t a[32];
+            __syncwarp();
+            tmem_ld_32x32(taddr + c * 32, a);
             tmem_ld_wait();
+            if constexpr (kPlanes == 3) {
+              uint32_t ca[32];
+              tmem_ld_32x32(taddr + kUmmaN + c * 32, ca);
+              tmem_ld_wait();
 #pragma unroll
-            for (int i = 0; i < 32; ++i) a[i] = __float_as_uint(__uint_as_float(a[i]) + __uint_as_float(ca[i]));
-          }
-          if (c == kUmmaN / 32 - 1) release_acc();
-          const int col0 = col_base + c * 32;
-          if (col0 < p.H) {
-            float o[32];
-            if (parts != nullptr) {
-              const float* q0 = parts + c * 32 * kTileM + row_in_tile;
-#pragma unroll
-              for (int i = 0; i < 32; ++i) o[i] = __ldcg(q0 + i * kTileM);
-              for (int pp = 1; pp < t.nparts - 1; ++pp) {
-                const float* qp = q0 + static_cast<size_t>(pp) * (kTileM * kUmmaN);
-#pragma unroll
-                for (int i = 0; i < 32; ++i) o[i] = __fadd_rn(o[i], __ldcg(qp + i * kTileM));
-              }
-#pragma unroll
-              for (int i = 0; i < 32; ++i) o[i] = __fadd_rn(o[i], __uint_as_float(a[i]));
-            } else {
-#pragma unroll
-              for (int i = 0; i < 32; ++i) o[i] = __uint_as_float(a[i]);
+              for (int i = 0; i < 32; ++i) a[i] = __float_as_uint(__uint_as_float(a[i]) + __uint_as_float(ca[i]));
             }
-            if (valid) {
+            if (c == kUmmaN / 32 - 1) release_acc();
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+              __stcg(mine + (c * 8 + j) * kTileM,
+                     make_float4(__uint_as_float(a[4 * j]), __uint_as_float(a[4 * j + 1]),
+                                 __uint_as_float(a[4 * j + 2]), __uint_as_float(a[4 * j + 3])));
+          }
+          // every lane's stores happen before the barrier, the barrier before lane 0's release;
+          // lane 0's acquire before the second barrier, that barrier before every lane's loads
+          __syncwarp();
+          uint32_t before = 0;
+          if (lane == 0) before = atom_add_acq_rel_gpu(p.split_done + t.split_idx * 4 + quad, 1u);
+          before = __shfl_sync(0xffffffffu, before, 0);
+          __syncwarp();
+          finish = before == static_cast<uint32_t>(t.nparts - 1);
+        }
+        if (finish) {
+          uint32_t meta = 0;
+          if (valid) meta = __ldcg(reinterpret_cast<const uint32_t*>(self + p.lay.landing_meta) + row);
+          const int src = static_cast<int>(meta >> kMetaSrcShift);
+          const uint32_t ret_row = meta & ((1u << kMetaSrcShift) - 1);
+          char* orow = p.peers[valid ? src : p.rank] + p.lay.ret + static_cast<size_t>(ret_row) * p.H * EB;
+          const int col_base = t.n * kUmmaN;
+          const float4* parts = reinterpret_cast<const float4*>(
+                                    p.split_scratch + static_cast<size_t>(t.split_idx) * p.split_parts * kTileFloats) +
+                                row_in_tile;
+          auto finish_chunk = [&](int c, float (&o)[32]) {   // bias, rounding, the row's 32 columns
+            const int col0 = col_base + c * 32;
+            if (valid && col0 < p.H) {
 #pragma unroll
               for (int i = 0; i < 32; ++i)
                 o[i] += bias_at<T>(p.bias_down, static_cast<size_t>(t.lx) * p.H + col0 + i);
               store_result32<T>(orow, col0, o);
             }
+          };
+          if (!split) {
+#pragma unroll 1
+            for (int c = 0; c < kUmmaN / 32; ++c) {
+              uint32_t a[32];
+              __syncwarp();
+              tmem_ld_32x32(taddr + c * 32, a);
+              tmem_ld_wait();
+              if constexpr (kPlanes == 3) {
+                uint32_t ca[32];
+                tmem_ld_32x32(taddr + kUmmaN + c * 32, ca);
+                tmem_ld_wait();
+#pragma unroll
+                for (int i = 0; i < 32; ++i) a[i] = __float_as_uint(__uint_as_float(a[i]) + __uint_as_float(ca[i]));
+              }
+              if (c == kUmmaN / 32 - 1) release_acc();
+              float o[32];
+#pragma unroll
+              for (int i = 0; i < 32; ++i) o[i] = __uint_as_float(a[i]);
+              finish_chunk(c, o);
+            }
+          } else if (valid) {
+            // two chunks per step: the parked sums of both are in flight before either is added up
+#pragma unroll 1
+            for (int c = 0; c < kUmmaN / 32; c += 2) {
+              float o[2][32];
+#pragma unroll
+              for (int h = 0; h < 2; ++h) {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                  const float4 v = __ldcg(parts + ((c + h) * 8 + j) * kTileM);
+                  o[h][4 * j] = v.x; o[h][4 * j + 1] = v.y; o[h][4 * j + 2] = v.z; o[h][4 * j + 3] = v.w;
+                }
+              }
+              for (int pp = 1; pp < t.nparts; ++pp) {
+                const float4* q = parts + static_cast<size_t>(pp) * (kTileFloats / 4);
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+#pragma unroll
+                  for (int j = 0; j < 8; ++j) {
+                    const float4 v = __ldcg(q + ((c + h) * 8 + j) * kTileM);
+                    o[h][4 * j] = __fadd_rn(o[h][4 * j], v.x); o[h][4 * j + 1] = __fadd_rn(o[h][4 * j + 1], v.y);
+                    o[h][4 * j + 2] = __fadd_rn(o[h][4 * j + 2], v.z); o[h][4 * j + 3] = __fadd_rn(o[h][4 * j + 3], v.w);
+                  }
+                }
+              }
+              finish_chunk(c, o[0]);
+              finish_chunk(c + 1, o[1]);
+            }
+          }
+          if (warp == 2 && lane == 0) stamp_now(10);
+          // Tell every owner how many of its rows this warp just delivered: every lane's stores
+          // happen before the barrier, the barrier before lane 0's fence, and ONE fence orders them
+          // before all the counter updates that follow (a release per update would pay the
+          // system-wide fence once per source rank).
+          __syncwarp();
+          if (lane == 0) { if (W > 1) fence_acq_rel_sys(); else fence_acq_rel_gpu(); }
+          for (int s = 0; s < W; ++s) {
+            const unsigned b = __ballot_sync(0xffffffffu, valid && src == s);
+            if (lane == 0 && b != 0)
+              red_add_relaxed_sys(reinterpret_cast<uint32_t*>(p.peers[s] + p.lay.ret_arrived),
+                                  static_cast<uint32_t>(__popc(b)));
           }
         }
-        __syncwarp();
-        // tell every owner how many of its rows this warp just delivered
-        for (int s = 0; s < W; ++s) {
-          const unsigned b = __ballot_sync(0xffffffffu, valid && src == s);
-          if (lane == 0 && b != 0)
-            red_add_release_sys(reinterpret_cast<uint32_t*>(p.peers[s] + p.lay.ret_arrived),
-                                static_cast<uint32_t>(__popc(b)));
-        }
       }
+      if (warp == 2 && lane == 0) stamp_now(11);
       ++acc_it;
     }
   }
@@ -1015,7 +1085,9 @@ __device__ __forceinline__ void moe_forward_body(const MoeParams& p, const TmaMa
   stamp(5);
   if (tid == 0 && ctl->ok && *reinterpret_cast<volatile uint32_t*>(p.abort_word) == 0) {
     const uint32_t* ra = reinterpret_cast<const uint32_t*>(self + p.lay.ret_arrived);
-    if (!wait_counter_sys(ra, static_cast<uint32_t>(ctl->expected_ret), wc)) {
+    const bool in = W > 1 ? wait_counter_sys(ra, static_cast<uint32_t>(ctl->expected_ret), wc)
+                          : wait_counter_gpu(ra, static_cast<uint32_t>(ctl->expected_ret), wc);
+    if (!in) {
       fail(p, FMOE_PHASE_RETURN_ARRIVAL, ctl->expected_ret);
       ctl->ok = 0;
     }

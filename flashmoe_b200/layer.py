@@ -169,6 +169,18 @@ class MoELayer:
                "kernel": float((t[:, 7].max() - t[:, 0].min()) / 1e3)}
         out["exposed_comm_frac"] = (out["count_exchange"] + out["first_rows_wait"] + out["wait_returns"]) / \
             max(out["kernel"], 1e-9)
+        # the last task of a median CTA: accumulator ready -> rows stored -> owners told
+        ep = t[:, 9] > 0
+        if bool(ep.any()):
+            out["last_epilogue"] = [float(((t[ep, 10] - t[ep, 9]) / 1e3).median()),
+                                    float(((t[ep, 11] - t[ep, 10]) / 1e3).median())]
+        # when the CTAs drew their stop ticket and finished their last task, from the first CTA's
+        # start: 10th, 50th, 90th percentile and the last one (the spread is the closing wave)
+        t0 = t[:, 0].min()
+        for name, col in (("stop_drawn_at", 4), ("last_task_done_at", 5)):
+            v = ((t[:, col] - t0) / 1e3).sort().values
+            n = len(v)
+            out[name] = [float(v[n // 10]), float(v[n // 2]), float(v[(9 * n) // 10]), float(v[-1])]
         return out
 
     def geometry(self):

@@ -106,7 +106,7 @@ enum {
   FMOE_PHASE_NONE = 0, FMOE_PHASE_COUNTS = 1, FMOE_PHASE_DISPATCH_ARRIVAL = 2,
   FMOE_PHASE_GEMM0_DONE = 3, FMOE_PHASE_RETURN_ARRIVAL = 4, FMOE_PHASE_PIPE_FULL = 5,
   FMOE_PHASE_PIPE_EMPTY = 6, FMOE_PHASE_TMEM_FULL = 7, FMOE_PHASE_TMEM_EMPTY = 8,
-  FMOE_PHASE_TASK = 9, FMOE_PHASE_SPLIT_PARTS = 10
+  FMOE_PHASE_TASK = 9
 };
 
 /* --- context life cycle -------------------------------------------------------------- */
@@ -246,7 +246,8 @@ int fmoe_get_geometry(const fmoe_ctx* ctx, fmoe_geometry* out);
  *          (0 start, 1 all ranks' counts in, 2 tables built, 3 this CTA's share of the dispatch
  *           done, 4 last ticket drawn, 5 this CTA's last task finished, 6 all returns in,
  *           7 combine done, 8 first operand tiles of the CTA's first task landed (0: it had none),
- *           9..15 unused) */
+ *           9, 10, 11 the epilogue of the CTA's last task: accumulator ready, rows stored, owners
+ *           told; 12..15 unused) */
 int fmoe_debug_buffer(fmoe_ctx* ctx, int32_t which, void** ptr_out, size_t* bytes_out);
 
 #ifdef __cplusplus

@@ -3,7 +3,7 @@
 #include <cstdio>
 #include <cstring>
 
-#include "flashmoe/flashmoe.hpp"
+#include "flashmoe/flashmoe.cuh"   // the include path of the reference
 
 int main() {
   using namespace flashmoe;

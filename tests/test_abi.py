@@ -84,8 +84,8 @@ def test_workspace_bytes_follow_the_description_without_a_device():
     rows = W * S + (E // W) * 128
     assert rows * H * 2 + S * H * 2 <= b["symmetric"] <= rows * H * 2 + S * H * 2 + (1 << 20)
     # GEMM0 output, plus the fp32 partial sums of the GEMM1 tiles the closing wave cuts along K
-    # (160 tiles x 3 parked parts x 128 x 256 floats)
-    split = 160 * 3 * 128 * 256 * 4
+    # (160 tiles x 2 parts x 128 x 256 floats)
+    split = 160 * 2 * 128 * 256 * 4
     assert rows * I * 2 + split <= b["workspace"] <= rows * I * 2 + split + (4 << 20)
     one = flashmoe.get_workspace_bytes(arg, ep_world=1)
     assert one["symmetric"] < b["symmetric"]

@@ -273,11 +273,13 @@ def _launches():
 def _same_up_to_split_order(a, b):
     """A token's output depends on that token only.  Its bits may still differ between two batches:
     rows that fall into a GEMM1 tile of the closing wave have their K sum formed in parts (fp32, fixed
-    order), the others in one pass, and a permutation moves rows between the two kinds of tile.  So:
-    most elements identical, every element within two units in the last place of the 16-bit type."""
+    order), the others in one pass, and a permutation moves rows between the two kinds of tile.  An
+    expert's output row can therefore move by one unit in the last place of the 16-bit type, and a
+    token's output by that much times its combine weight.  So: most elements identical, and every
+    element within a few units in the last place of the larger of itself and a typical output."""
     assert (a == b).double().mean() >= 0.5
     diff = (a.double() - b.double()).abs()
-    bound = 2.0 ** -6 * b.double().abs() + 1e-5 * float(b.double().abs().max())
+    bound = 2.0 ** -6 * b.double().abs() + 2.0 ** -5 * float(b.double().pow(2).mean().sqrt())
     assert bool((diff <= bound).all()), float((diff / bound).max())
 
 

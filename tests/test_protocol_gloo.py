@@ -155,6 +155,57 @@ def test_a_rank_that_leaves_before_the_handle_exchange_is_noticed_on_the_host():
     assert msg.startswith("error"), msg
 
 
+def _rank_map_main(rank, world, port, q):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        cb.initialize()
+        res = {}
+        # (1) a permuted map over the whole world: EP rank p lives in process world - 1 - p
+        perm = [world - 1 - p for p in range(world)]
+        got = cb.exchange_by_rank_map(bytes([rank]) * 8, world - 1 - rank, perm)
+        res["permuted"] = [b[0] for b in got] == perm
+        # (2) EP groups smaller than the world: {0, 1} and {2, 3}, the second one listed backwards
+        groups = [[0, 1], [3, 2]]
+        mine = groups[0] if rank in groups[0] else groups[1]
+        got = cb.exchange_by_rank_map(bytes([100 + rank]) * 8, mine.index(rank), mine)
+        res["subset"] = [b[0] for b in got] == [100 + g for g in mine]
+        # (3) a map that does not describe this process is refused before anything is exchanged
+        try:
+            cb.exchange_by_rank_map(b"x", 0, [(rank + 1) % world])
+            res["refused"] = False
+        except ValueError:
+            res["refused"] = True
+        # (4) peers that disagree with the map: everyone claims EP rank 0 of a 2-rank group
+        try:
+            cb.exchange_by_rank_map(b"x", 0, [rank, (rank + 1) % world])
+            res["disagree"] = False
+        except ValueError:
+            res["disagree"] = True
+        q.put((rank, res))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_peer_handles_follow_rank_map():
+    """The handle exchange of `initialize` resolves peers through rank_map (the reference's
+    epRankToGlobalRank): a permuted map and EP groups smaller than the world give every rank its
+    own group's payloads in EP-rank order; inconsistent maps raise on the host."""
+    import socket
+    s = socket.socket(); s.bind(("127.0.0.1", 0)); port = s.getsockname()[1]; s.close()
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_rank_map_main, args=(r, 4, port, q)) for r in range(4)]
+    for p in procs:
+        p.start()
+    res = [q.get(timeout=120) for _ in procs]
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    for rank, r in res:
+        assert all(r.values()), (rank, r)
+
+
 def test_layout_matches_hand_computed_example():
     counts = [[3, 0, 130, 1], [2, 5, 0, 200]]
     lay = layout.build(counts, 1, [0, 0, 1, 1], ec=128, tiles_n0=2, tiles_n1=1, grid=1)
