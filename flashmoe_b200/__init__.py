@@ -10,12 +10,13 @@ swaps CUDA IPC handles between the ranks of the expert-parallel group.
 from __future__ import annotations
 
 import ctypes as C
+import os
 
 from . import _native as N
 from . import cb, reference, router
 from .cb import get_local_rank
 from .jit import (ActivationType, ContextHandle, DataType, ForwardArgs, InitArgs, MLPType,
-                  Topology, _get_compiled)
+                  Topology, _get_compiled, specialised_library)
 
 __all__ = ["initialize", "forward", "finalize", "get_workspace_bytes", "router", "reference", "cb", "get_local_rank", "InitArgs",
            "ForwardArgs", "ContextHandle", "Topology", "MLPType", "ActivationType", "DataType",
@@ -58,6 +59,9 @@ class _MoEModule:
                     N.check(self._lib.fmoe_symm_import(ctx, peer, buf), "initialize (import)")
         N.check(self._lib.fmoe_ctx_commit(ctx), "initialize (commit)")
         return ctx.value
+
+    def load_specialised(self, raw_ctx, path) -> None:
+        N.check(self._lib.fmoe_ctx_load_specialised(C.c_void_p(raw_ctx), str(path).encode()), "load_specialised")
 
     def forward(self, raw_ctx, tokens, expert_counts, local_expert_up, local_expert_up_v, local_bias_up,
                 local_bias_up_v, local_expert_down, local_bias_down, moe_out, swish_alpha, swish_beta,
@@ -133,6 +137,12 @@ def initialize(arg: InitArgs) -> ContextHandle:
                          ep_world=arg.ep_world, my_pe=arg.my_pe, ep_rank=arg.ep_rank,
                          local_rank=arg.device_id, num_local_experts=arg.num_local_experts,
                          expert_map=arg.expert_map, rank_map=arg.rank_map, stream_ptr=arg.stream_ptr)
+    # the kernel specialised for this description, when the cache holds it (or FMOE_JIT=1 builds it);
+    # FMOE_JIT=off keeps the generic kernel
+    if os.environ.get("FMOE_JIT", "0") != "off":
+        spec = specialised_library(arg, pair=bool(mod.geometry(ctx).cta_pairs))
+        if spec is not None:
+            mod.load_specialised(ctx, spec)
     cb.sync_all(arg.stream_ptr)
     return ContextHandle(mod, ctx)
 

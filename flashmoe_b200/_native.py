@@ -16,7 +16,7 @@ SRC_DIR = PKG_DIR / "csrc"
 LIB_PATH = PKG_DIR / "lib" / "libflashmoe_b200.so"
 SOURCES = ("router.cu", "moe_kernel.cu", "abi.cu")
 NVCC_FLAGS = ("-std=c++17", "-O3", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo",
-              "-Xcompiler", "-fPIC", "-shared")
+              "-Xcompiler", "-fPIC", "-shared", "-ldl")
 
 IPC_HANDLE_BYTES = 64
 MAX_WORLD = 8
@@ -55,7 +55,9 @@ class Geometry(C.Structure):
     _fields_ = [(n, C.c_int32) for n in (
         "tile_m", "tile_n0", "tile_n1", "tile_k", "stages", "round_ec", "landing_rows", "grid",
         "threads", "smem_bytes", "cta_pairs", "split_parts")] + [("symm_bytes", C.c_int64),
-                                                               ("workspace_bytes", C.c_int64)]
+                                                                  ("workspace_bytes", C.c_int64),
+                                                                  ("specialised", C.c_int32),
+                                                                  ("reserved", C.c_int32)]
 
 
 # name -> (restype, argtypes); the single source of truth for the symbol-export test too
@@ -74,6 +76,7 @@ SIGNATURES = {
     "fmoe_ctx_destroy": (C.c_int, [C.c_void_p, C.c_void_p]),
     "fmoe_forward": (C.c_int, [C.c_void_p, C.POINTER(ForwardArgsC), C.c_void_p]),
     "fmoe_weights_changed": (C.c_int, [C.c_void_p]),
+    "fmoe_ctx_load_specialised": (C.c_int, [C.c_void_p, C.c_char_p]),
     "fmoe_router_create": (C.c_int, [C.POINTER(ModelDesc), C.c_int32, C.c_int32, C.c_void_p,
                                      C.POINTER(C.c_void_p)]),
     "fmoe_router_forward": (C.c_int, [C.c_void_p, C.c_void_p, C.POINTER(RouterArgsC), C.c_void_p]),

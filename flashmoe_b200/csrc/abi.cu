@@ -3,6 +3,8 @@
 // construction and the launches.  It plays the role of the reference's bootstrap
 // (csrc/include/flashmoe/bootstrap.cuh:197-474) and of its pybind glue
 // (flashmoe/bindings.py:68-185, 238-315), with CUDA IPC in place of the NVSHMEM heap.
+#include <dlfcn.h>
+
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
@@ -115,6 +117,9 @@ struct fmoe_ctx {
   char* wsplit = nullptr;               // fp32 layers: BF16 planes of up | up_v | down
   size_t wsplit_up = 0, wsplit_up_v = 0, wsplit_down = 0;
   const void* wsplit_src[3] = {nullptr, nullptr, nullptr};   // the weight set those planes were made from
+  // a library built for exactly this layer's description (fmoe_ctx_load_specialised), or none
+  void* spec_handle = nullptr;
+  int (*spec_launch)(const void*, const void*, int, size_t, void*) = nullptr;
 };
 
 struct fmoe_router {
@@ -259,6 +264,7 @@ void free_ctx(fmoe_ctx* c) {
   if (c->wsplit) cudaFree(c->wsplit);
   if (c->stage_tokens) cudaFree(c->stage_tokens);
   if (c->stage_out) cudaFree(c->stage_out);
+  if (c->spec_handle) dlclose(c->spec_handle);
   if (c->pipe.ready) {
     for (int i = 0; i < 2; ++i) {
       cudaFree(c->pipe.tokens[i]); cudaFree(c->pipe.out[i]);
@@ -599,7 +605,54 @@ int fmoe_forward(fmoe_ctx* ctx, const fmoe_forward_args* a, void* stream) {
   p.tokens = a->tokens; p.expert_counts = a->expert_counts;
   p.bias_up = a->local_bias_up; p.bias_up_v = a->local_bias_up_v; p.bias_down = a->local_bias_down;
   p.out = a->moe_out; p.alpha = a->swish_alpha; p.beta = a->swish_beta;
-  FMOE_CUDA(launch_moe(p, ctx->maps, ctx->geo.grid, ctx->geo.smem_bytes, st));
+  if (ctx->spec_launch != nullptr) {
+    const cudaError_t e = static_cast<cudaError_t>(ctx->spec_launch(&p, ctx->maps, ctx->geo.grid,
+                                                                     static_cast<size_t>(ctx->geo.smem_bytes), st));
+    ++g_launches;
+    if (e != cudaSuccess)
+      return set_error(FMOE_ERR_CUDA, std::string("specialised launch: ") + cudaGetErrorName(e) + " (" +
+                                          cudaGetErrorString(e) + ")");
+  } else {
+    const cudaError_t e = launch_moe(p, ctx->maps, ctx->geo.grid, ctx->geo.smem_bytes, st);
+    ++g_launches;
+    if (e != cudaSuccess)
+      return set_error(FMOE_ERR_CUDA, std::string("launch: ") + cudaGetErrorName(e) + " (" + cudaGetErrorString(e) + ")");
+  }
+  return FMOE_OK;
+}
+
+int fmoe_ctx_load_specialised(fmoe_ctx* ctx, const char* path) {
+  if (ctx == nullptr || path == nullptr) return set_error(FMOE_ERR_INVALID_ARG, "null argument");
+  void* h = dlopen(path, RTLD_NOW | RTLD_LOCAL);
+  if (h == nullptr) return set_error(FMOE_ERR_INVALID_ARG, std::string("cannot load ") + path + ": " + dlerror());
+  auto info = reinterpret_cast<int (*)(int32_t*)>(dlsym(h, "fmoe_spec_info"));
+  auto prepare = reinterpret_cast<int (*)(size_t)>(dlsym(h, "fmoe_spec_prepare"));
+  auto launch = reinterpret_cast<int (*)(const void*, const void*, int, size_t, void*)>(dlsym(h, "fmoe_spec_launch"));
+  if (info == nullptr || prepare == nullptr || launch == nullptr) {
+    dlclose(h);
+    return set_error(FMOE_ERR_INVALID_ARG, std::string(path) + " is not a specialised flashmoe_b200 kernel library");
+  }
+  int32_t v[8] = {};
+  info(v);
+  const fmoe_model_desc& m = ctx->model;
+  const bool same = v[0] == m.token_dim && v[1] == m.ffn_size && v[2] == m.top_k &&
+                    v[3] == (m.mlp_type == FMOE_MLP_GATED ? 1 : 0) && v[4] == m.act_type && v[5] == m.data_type &&
+                    v[6] == ctx->params.pair && v[7] == static_cast<int32_t>(sizeof(MoeParams));
+  if (!same) {
+    dlclose(h);
+    return set_error(FMOE_ERR_INVALID_ARG, std::string(path) + " was built for another layer description (or another "
+                                           "version of the library)");
+  }
+  cudaError_t ce = cudaSetDevice(ctx->device);
+  if (ce == cudaSuccess) ce = static_cast<cudaError_t>(prepare(static_cast<size_t>(ctx->geo.smem_bytes)));
+  if (ce != cudaSuccess) {
+    dlclose(h);
+    return set_error(FMOE_ERR_CUDA, std::string("specialised kernel set-up: ") + cudaGetErrorString(ce));
+  }
+  if (ctx->spec_handle != nullptr) dlclose(ctx->spec_handle);
+  ctx->spec_handle = h;
+  ctx->spec_launch = launch;
+  ctx->geo.specialised = 1;
   return FMOE_OK;
 }
 

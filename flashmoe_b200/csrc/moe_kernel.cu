@@ -256,9 +256,16 @@ __host__ __device__ inline size_t tables_ints(int W, int E, int nLx) {
 // kPair = false: every CTA on its own 128 x 256 tile with the whole B tile (4 stages of 48 KB):
 // more weight bytes in flight per SM, which is what counts when experts hold <= 128 rows and the
 // layer streams weights from HBM.
-template <typename T, bool kPair>
+template <typename T, bool kPair, typename Spec>
 __device__ __forceinline__ void moe_forward_body(const MoeParams& p, const TmaMaps& maps) {
   extern __shared__ uint8_t smem_raw[];
+  // the layer's shape: launch parameters in the generic build, constants in a specialised one
+  const int H_ = Spec::kFixed ? Spec::kH : p.H, I_ = Spec::kFixed ? Spec::kI : p.I;
+  const int K_ = Spec::kFixed ? Spec::kTopK : p.k;
+  const bool gated_ = Spec::kFixed ? Spec::kGated : p.gated != 0;
+  const int act_ = Spec::kFixed ? Spec::kAct : p.act;
+  const int tiles_n0_ = Spec::kFixed ? (Spec::kI + (Spec::kGated ? 128 : 256) - 1) / (Spec::kGated ? 128 : 256) : p.tiles_n0;
+  const int tiles_n1_ = Spec::kFixed ? (Spec::kH + 255) / 256 : p.tiles_n1;
   constexpr int NS = kPair ? 6 : 4;                                   // ring depth
   constexpr uint32_t SA = kStageABytes;                               // A tile of this CTA
   constexpr uint32_t SB = kPair ? kStageABytes : 2 * kStageABytes;    // B rows this CTA loads
@@ -298,8 +305,8 @@ __device__ __forceinline__ void moe_forward_body(const MoeParams& p, const TmaMa
   char* const self = p.peers[p.rank];
   constexpr int EB = Elem<T>::kBytes;     // bytes per element of tokens, return rows and output
   constexpr int kPlanes = Elem<T>::kPlanes;  // BF16 planes per GEMM operand
-  const size_t landing_plane = static_cast<size_t>(p.landing_rows) * p.H * 2;
-  const size_t y_plane = static_cast<size_t>(p.landing_rows) * p.I * 2;
+  const size_t landing_plane = static_cast<size_t>(p.landing_rows) * H_ * 2;
+  const size_t y_plane = static_cast<size_t>(p.landing_rows) * I_ * 2;
 
   // ---- set-up: barriers, TMEM, epoch ---------------------------------------------------
   if (tid == 0) {
@@ -411,7 +418,7 @@ __device__ __forceinline__ void moe_forward_body(const MoeParams& p, const TmaMa
       tb.send_pref[E] = sp;
       ctl->send_rows = sp;
       ctl->class0_experts = e0;
-      ctl->expected_ret = sp * p.tiles_n1;   // one count per returned row and N1 tile
+      ctl->expected_ret = sp * tiles_n1_;   // one count per returned row and N1 tile
     }
   }
   __syncthreads();
@@ -436,8 +443,8 @@ __device__ __forceinline__ void moe_forward_body(const MoeParams& p, const TmaMa
       ri.pos = lo;
       ri.row = row;
       ri.token = p.table[static_cast<size_t>(e) * p.round_ec + (row - tb.send_pref[lo])].token;
-      for (int c = 0; c < p.k; ++c)
-        if (p.routes[static_cast<size_t>(ri.token) * p.k + c].expert == e) { ri.choice = c; break; }
+      for (int c = 0; c < K_; ++c)
+        if (p.routes[static_cast<size_t>(ri.token) * K_ + c].expert == e) { ri.choice = c; break; }
     }
     return ri;
   };
@@ -512,7 +519,7 @@ __device__ __forceinline__ void moe_forward_body(const MoeParams& p, const TmaMa
   // GEMM0 tiles it depends on are long finished: G0(0..lag-1), G0(lag), G1(0), G0(lag+1), G1(1), ...
   if (ctl->ok) {
     for (int t = 1 + tid; t < nLx; t += kThreads)
-      if (tb.lx_mt0[t] * p.tiles_n0 >= 2 * static_cast<int>(gridDim.x)) atomicMin(&ctl->lag, t);
+      if (tb.lx_mt0[t] * tiles_n0_ >= 2 * static_cast<int>(gridDim.x)) atomicMin(&ctl->lag, t);
   }
   __syncthreads();
   if (ctl->ok) {
@@ -525,13 +532,13 @@ __device__ __forceinline__ void moe_forward_body(const MoeParams& p, const TmaMa
       const int i0 = i + max(0, i - lag);                                   // G0(i)
       const int s1 = i + lag;
       const int i1 = min(s1, nLx) + i + (s1 < nLx ? 1 : 0);                 // G1(i)
-      tb.seg_first[i0] = groups * p.tiles_n0; tb.seg_kind[i0] = kTaskGemm0; tb.seg_lx[i0] = i;
-      tb.seg_whole[i0] = groups * p.tiles_n0;
+      tb.seg_first[i0] = groups * tiles_n0_; tb.seg_kind[i0] = kTaskGemm0; tb.seg_lx[i0] = i;
+      tb.seg_whole[i0] = groups * tiles_n0_;
       // The last `split_tiles` GEMM1 tiles of the task order (about one wave of CTAs) are cut along
       // K into `split_parts` tickets each, so that the kernel ends on short tickets: `after` tiles
       // follow this segment, so its last (split_tiles - after) tiles are cut.  Never in pair mode.
-      const int tiles = groups * p.tiles_n1;
-      const int after = (tb.lx_mt0[nLx] - tb.lx_mt0[i + 1]) * p.tiles_n1;   // kGroup == 1 when splitting
+      const int tiles = groups * tiles_n1_;
+      const int after = (tb.lx_mt0[nLx] - tb.lx_mt0[i + 1]) * tiles_n1_;   // kGroup == 1 when splitting
       const int cut = (kPair || p.split_parts <= 1) ? 0 : max(0, min(tiles, p.split_tiles - after));
       tb.seg_first[i1] = (tiles - cut) + cut * p.split_parts;
       tb.seg_whole[i1] = tiles - cut;
@@ -557,7 +564,7 @@ __device__ __forceinline__ void moe_forward_body(const MoeParams& p, const TmaMa
   // own M tile only (per source, on disp_arrived) and the dispatch depends on no ticket, so the
   // order stays deadlock-free; the first epilogue is due one whole main loop after the first MMA.
   auto send_rows = [&](const int v0, const RowInfo ri) {   // list entries v0 .. v0 + 31
-    const int vecs = p.H * EB / 16;
+    const int vecs = H_ * EB / 16;
     const uint4* tok_base = static_cast<const uint4*>(p.tokens);
     const int n = min(32, n0 + n1 - v0);
     for (int i = 0; i < n; ++i) {
@@ -601,7 +608,7 @@ __device__ __forceinline__ void moe_forward_body(const MoeParams& p, const TmaMa
       }
       if (lane == 0)
         reinterpret_cast<uint32_t*>(peer + p.lay.landing_meta)[drow] =
-            (static_cast<uint32_t>(p.rank) << kMetaSrcShift) | (token * p.k + choice);
+            (static_cast<uint32_t>(p.rank) << kMetaSrcShift) | (token * K_ + choice);
     }
     // Count the rows in at their owners, one update per expert.  Every lane's stores happen before
     // the barrier, the barrier before lane 0's fence, and that ONE fence orders them before all the
@@ -628,7 +635,7 @@ __device__ __forceinline__ void moe_forward_body(const MoeParams& p, const TmaMa
   // cluster of 2, on the two SMs of one TPC) work on one 256 x 256 output tile: each loads its own
   // 128 rows of A and its own half of the B tile, the leader issues tcgen05.mma.cta_group::2, each
   // keeps its 128 rows of the accumulator in its own TMEM.
-  const int nk0 = p.H / kTileK, nk1 = p.I / kTileK;
+  const int nk0 = H_ / kTileK, nk1 = I_ / kTileK;
   // plane pairs (A plane, B plane) per K block, smallest contributions first
   constexpr int kPairs = kPlanes == 1 ? 1 : 6;
   constexpr int kBufs = kPlanes == 1 ? kAccBufs : 1;   // fp32 layers use both TMEM halves per task
@@ -657,8 +664,8 @@ __device__ __forceinline__ void moe_forward_body(const MoeParams& p, const TmaMa
       idx = whole + j / p.split_parts;
       t.part = j - (idx - whole) * p.split_parts;
       t.nparts = p.split_parts;
-      const int after = (tb.lx_mt0[nLx] - tb.lx_mt0[lx + 1]) * p.tiles_n1;
-      t.split_idx = after + (groups * p.tiles_n1 - 1 - idx);
+      const int after = (tb.lx_mt0[nLx] - tb.lx_mt0[lx + 1]) * tiles_n1_;
+      t.split_idx = after + (groups * tiles_n1_ - 1 - idx);
     }
     const int n2 = idx / groups;
     t.n = n2;
@@ -712,7 +719,7 @@ __device__ __forceinline__ void moe_forward_body(const MoeParams& p, const TmaMa
             const int mts = tb.lx_mt0[t.lx + 1] - tb.lx_mt0[t.lx];
             for (int q = 0; q < kGroup && ok; ++q) {
               if (t.m_in_expert + q >= mts) break;
-              if (!wait_counter_gpu(p.gemm0_done + t.mt + q, static_cast<uint32_t>(4 * p.tiles_n0), wc)) {
+              if (!wait_counter_gpu(p.gemm0_done + t.mt + q, static_cast<uint32_t>(4 * tiles_n0_), wc)) {
                 fail(p, FMOE_PHASE_GEMM0_DONE, t.mt + q); ok = false;
               }
             }
@@ -740,17 +747,17 @@ __device__ __forceinline__ void moe_forward_body(const MoeParams& p, const TmaMa
         // the B tile as two halves of 128 rows: GEMM0 gated = gate rows | up rows.  In a pair the
         // leader loads the first half and the follower the second; alone, a CTA loads both.
         const CUtensorMap* map_b0 = g0 ? &maps.up : &maps.down;
-        const CUtensorMap* map_b1 = g0 ? (p.gated ? &maps.up_v : &maps.up) : &maps.down;
+        const CUtensorMap* map_b1 = g0 ? (gated_ ? &maps.up_v : &maps.up) : &maps.down;
         int brow0, brow1;
         if (g0) {
-          if (p.gated) { brow0 = t.lx * p.I + t.n * 128; brow1 = brow0; }
-          else { brow0 = t.lx * p.I + t.n * 256; brow1 = brow0 + 128; }
+          if (gated_) { brow0 = t.lx * I_ + t.n * 128; brow1 = brow0; }
+          else { brow0 = t.lx * I_ + t.n * 256; brow1 = brow0 + 128; }
         } else {
-          brow0 = t.lx * p.H + t.n * kUmmaN; brow1 = brow0 + 128;
+          brow0 = t.lx * H_ + t.n * kUmmaN; brow1 = brow0 + 128;
         }
         const CUtensorMap* map_b = leader ? map_b0 : map_b1;
         const int brow = leader ? brow0 : brow1;
-        const int b_plane_rows = g0 ? nLx * p.I : nLx * p.H;   // rows of one BF16 plane of the weights
+        const int b_plane_rows = g0 ? nLx * I_ : nLx * H_;   // rows of one BF16 plane of the weights
         const int kb_begin = nk * t.part / t.nparts, kb_end = nk * (t.part + 1) / t.nparts;
         for (int kb = kb_begin; kb < kb_end && ok; ++kb) {
           // the next ticket is drawn while the last stages of this task are still being consumed,
@@ -881,8 +888,8 @@ __device__ __forceinline__ void moe_forward_body(const MoeParams& p, const TmaMa
       };
 
       if (t.kind == kTaskGemm0) {
-        char* yrow = static_cast<char*>(p.y) + static_cast<size_t>(row) * p.I * 2;
-        if (p.gated) {
+        char* yrow = static_cast<char*>(p.y) + static_cast<size_t>(row) * I_ * 2;
+        if (gated_) {
           const int col_base = t.n * 128;
 #pragma unroll 1
           for (int c = 0; c < 4; ++c) {
@@ -904,13 +911,13 @@ __device__ __forceinline__ void moe_forward_body(const MoeParams& p, const TmaMa
             }
             if (c == 3) release_acc();
             const int col0 = col_base + c * 32;
-            if (valid && col0 < p.I) {
+            if (valid && col0 < I_) {
               float y[32];
 #pragma unroll
               for (int i = 0; i < 32; ++i) {
-                const size_t bi = static_cast<size_t>(t.lx) * p.I + col0 + i;
+                const size_t bi = static_cast<size_t>(t.lx) * I_ + col0 + i;
                 const float gate = (__uint_as_float(g[i]) + bias_at<T>(p.bias_up, bi)) * p.beta;
-                const float tt = Cvt<T>::round(p.alpha * activate_t<EB == 4>(gate, p.act));
+                const float tt = Cvt<T>::round(p.alpha * activate_t<EB == 4>(gate, act_));
                 const float v = __uint_as_float(u[i]) + bias_at<T>(p.bias_up_v, bi);
                 y[i] = v * tt;
               }
@@ -934,12 +941,12 @@ __device__ __forceinline__ void moe_forward_body(const MoeParams& p, const TmaMa
             }
             if (c == 7) release_acc();
             const int col0 = col_base + c * 32;
-            if (valid && col0 < p.I) {
+            if (valid && col0 < I_) {
               float y[32];
 #pragma unroll
               for (int i = 0; i < 32; ++i) {
-                const size_t bi = static_cast<size_t>(t.lx) * p.I + col0 + i;
-                y[i] = activate_t<EB == 4>(__uint_as_float(a[i]) + bias_at<T>(p.bias_up, bi), p.act);
+                const size_t bi = static_cast<size_t>(t.lx) * I_ + col0 + i;
+                y[i] = activate_t<EB == 4>(__uint_as_float(a[i]) + bias_at<T>(p.bias_up, bi), act_);
               }
               store_operand32<T>(yrow, col0, y, y_plane);
             }
@@ -995,17 +1002,17 @@ __device__ __forceinline__ void moe_forward_body(const MoeParams& p, const TmaMa
           if (valid) meta = __ldcg(reinterpret_cast<const uint32_t*>(self + p.lay.landing_meta) + row);
           const int src = static_cast<int>(meta >> kMetaSrcShift);
           const uint32_t ret_row = meta & ((1u << kMetaSrcShift) - 1);
-          char* orow = p.peers[valid ? src : p.rank] + p.lay.ret + static_cast<size_t>(ret_row) * p.H * EB;
+          char* orow = p.peers[valid ? src : p.rank] + p.lay.ret + static_cast<size_t>(ret_row) * H_ * EB;
           const int col_base = t.n * kUmmaN;
           const float4* parts = reinterpret_cast<const float4*>(
                                     p.split_scratch + static_cast<size_t>(t.split_idx) * p.split_parts * kTileFloats) +
                                 row_in_tile;
           auto finish_chunk = [&](int c, float (&o)[32]) {   // bias, rounding, the row's 32 columns
             const int col0 = col_base + c * 32;
-            if (valid && col0 < p.H) {
+            if (valid && col0 < H_) {
 #pragma unroll
               for (int i = 0; i < 32; ++i)
-                o[i] += bias_at<T>(p.bias_down, static_cast<size_t>(t.lx) * p.H + col0 + i);
+                o[i] += bias_at<T>(p.bias_down, static_cast<size_t>(t.lx) * H_ + col0 + i);
               store_result32<T>(orow, col0, o);
             }
           };
@@ -1096,16 +1103,16 @@ __device__ __forceinline__ void moe_forward_body(const MoeParams& p, const TmaMa
   stamp(6);
   if (ctl->ok && *reinterpret_cast<volatile uint32_t*>(p.abort_word) == 0) {
     const int G = gridDim.x * (kThreads / 32);
-    const int vecs = p.H * EB / 16;
+    const int vecs = H_ * EB / 16;
     const uint4* ret = reinterpret_cast<const uint4*>(self + p.lay.ret);
     uint4* out = static_cast<uint4*>(p.out);
     constexpr int kPer = 16 / EB;   // elements per 16-byte vector
     for (int tkn = blockIdx.x * (kThreads / 32) + warp; tkn < p.S; tkn += G) {
       // lane j holds the token's j-th route; a dropped pair gets weight-slot -1
       Route mine{0, p.EC, 0.0f, 0};
-      if (lane < p.k) mine = p.routes[static_cast<size_t>(tkn) * p.k + lane];
-      const unsigned live = __ballot_sync(0xffffffffu, lane < p.k && mine.slot < p.EC);
-      if (p.k == 1) {
+      if (lane < K_) mine = p.routes[static_cast<size_t>(tkn) * K_ + lane];
+      const unsigned live = __ballot_sync(0xffffffffu, lane < K_ && mine.slot < p.EC);
+      if (K_ == 1) {
         if (live & 1u) {
           const uint4* src = ret + static_cast<size_t>(tkn) * vecs;
           uint4* dst = out + static_cast<size_t>(tkn) * vecs;
@@ -1127,16 +1134,16 @@ __device__ __forceinline__ void moe_forward_body(const MoeParams& p, const TmaMa
           // rows of four choices are fetched together (eight loads in flight per lane), then
           // accumulated in choice order.  (No warp shuffle in here: with H < 256 only some lanes
           // run this loop.)
-          for (int j0 = 0; j0 < p.k; j0 += 4) {
+          for (int j0 = 0; j0 < K_; j0 += 4) {
             uint4 x[4][2];
             float wj[4];
 #pragma unroll
             for (int jj = 0; jj < 4; ++jj) {
               const int j = j0 + jj;
               wj[jj] = 0.0f;
-              if (j < p.k && ((live >> j) & 1u)) {
-                wj[jj] = p.routes[static_cast<size_t>(tkn) * p.k + j].weight;
-                const uint4* src = ret + (static_cast<size_t>(tkn) * p.k + j) * vecs;
+              if (j < K_ && ((live >> j) & 1u)) {
+                wj[jj] = p.routes[static_cast<size_t>(tkn) * K_ + j].weight;
+                const uint4* src = ret + (static_cast<size_t>(tkn) * K_ + j) * vecs;
 #pragma unroll
                 for (int u = 0; u < 2; ++u) if (v0 + 32 * u < vecs) x[jj][u] = __ldcg(src + v0 + 32 * u);
               }
@@ -1144,7 +1151,7 @@ __device__ __forceinline__ void moe_forward_body(const MoeParams& p, const TmaMa
 #pragma unroll
             for (int jj = 0; jj < 4; ++jj) {
               const int j = j0 + jj;
-              if (!(j < p.k && ((live >> j) & 1u))) continue;
+              if (!(j < K_ && ((live >> j) & 1u))) continue;
 #pragma unroll
               for (int u = 0; u < 2; ++u) {
                 const uint32_t w4[4] = {x[jj][u].x, x[jj][u].y, x[jj][u].z, x[jj][u].w};
@@ -1201,15 +1208,35 @@ __device__ __forceinline__ void moe_forward_body(const MoeParams& p, const TmaMa
   }
 }
 
+// The generic build reads the layer's shape from the launch parameters.  A specialised build
+// (-DFMOE_SPEC, one per model description, the counterpart of the reference's per-model JIT
+// module, flashmoe/bindings.py:34-46) fixes H, I, top-k, the MLP type and the activation at compile
+// time: loop bounds and the epilogue's branches fold away.
+struct GenericSpec {
+  static constexpr bool kFixed = false;
+  static constexpr int kH = 0, kI = 0, kTopK = 0, kAct = 0;
+  static constexpr bool kGated = false;
+};
+#ifdef FMOE_SPEC
+struct FixedSpec {
+  static constexpr bool kFixed = true;
+  static constexpr int kH = FMOE_SPEC_H, kI = FMOE_SPEC_I, kTopK = FMOE_SPEC_K, kAct = FMOE_SPEC_ACT;
+  static constexpr bool kGated = FMOE_SPEC_GATED != 0;
+};
+using KernelSpec = FixedSpec;
+#else
+using KernelSpec = GenericSpec;
+#endif
+
 template <typename T>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
 moe_forward_kernel_pair(const __grid_constant__ MoeParams p, const __grid_constant__ TmaMaps maps) {
-  moe_forward_body<T, true>(p, maps);
+  moe_forward_body<T, true, KernelSpec>(p, maps);
 }
 template <typename T>
 __global__ void __launch_bounds__(kThreads, 1)
 moe_forward_kernel(const __grid_constant__ MoeParams p, const __grid_constant__ TmaMaps maps) {
-  moe_forward_body<T, false>(p, maps);
+  moe_forward_body<T, false, KernelSpec>(p, maps);
 }
 
 }  // namespace
@@ -1219,12 +1246,32 @@ size_t moe_smem_bytes(int W, int E, int nLx) {
          tables_ints(W, E, nLx) * sizeof(int) + 64;
 }
 
+#ifdef FMOE_SPEC
+// a specialised build holds exactly one kernel: its element type and its form (alone / pairs)
+#if FMOE_SPEC_DT == 2
+using SpecElement = float;
+#elif FMOE_SPEC_DT == 1
+using SpecElement = __half;
+#else
+using SpecElement = __nv_bfloat16;
+#endif
+#if FMOE_SPEC_PAIR
+#define FMOE_SPEC_KERNEL moe_forward_kernel_pair<SpecElement>
+#else
+#define FMOE_SPEC_KERNEL moe_forward_kernel<SpecElement>
+#endif
+#endif
+
 cudaError_t moe_prepare_kernel(size_t smem) {
   const int n = static_cast<int>(smem);
   cudaError_t e = cudaSuccess;
   auto set = [&](auto kern) { if (e == cudaSuccess) e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, n); };
+#ifdef FMOE_SPEC
+  set(FMOE_SPEC_KERNEL);
+#else
   set(moe_forward_kernel<__nv_bfloat16>); set(moe_forward_kernel<__half>); set(moe_forward_kernel<float>);
   set(moe_forward_kernel_pair<__nv_bfloat16>); set(moe_forward_kernel_pair<__half>); set(moe_forward_kernel_pair<float>);
+#endif
   return e;
 }
 
@@ -1274,6 +1321,9 @@ cudaError_t launch_moe(const MoeParams& p, const CUtensorMap* maps, int grid, si
   cfg.attrs = attr;
   cfg.numAttrs = 1;
   cudaError_t e;
+#ifdef FMOE_SPEC
+  e = cudaLaunchKernelEx(&cfg, FMOE_SPEC_KERNEL, p, m);
+#else
   if (p.pair) {
     if (p.elem_bytes == 4) e = cudaLaunchKernelEx(&cfg, moe_forward_kernel_pair<float>, p, m);
     else if (p.ab_format == 1) e = cudaLaunchKernelEx(&cfg, moe_forward_kernel_pair<__nv_bfloat16>, p, m);
@@ -1283,8 +1333,27 @@ cudaError_t launch_moe(const MoeParams& p, const CUtensorMap* maps, int grid, si
     else if (p.ab_format == 1) e = cudaLaunchKernelEx(&cfg, moe_forward_kernel<__nv_bfloat16>, p, m);
     else e = cudaLaunchKernelEx(&cfg, moe_forward_kernel<__half>, p, m);
   }
-  ++g_launches;
+#endif
   return e;
 }
 
 }  // namespace fmoe
+
+#ifdef FMOE_SPEC
+// What a specialised library exports (loaded by fmoe_ctx_load_specialised): its constants, so the
+// host can check them against the context, and the two calls that replace the generic ones.
+extern "C" {
+int fmoe_spec_info(int32_t* out8) {
+  out8[0] = FMOE_SPEC_H; out8[1] = FMOE_SPEC_I; out8[2] = FMOE_SPEC_K; out8[3] = FMOE_SPEC_GATED;
+  out8[4] = FMOE_SPEC_ACT; out8[5] = FMOE_SPEC_DT; out8[6] = FMOE_SPEC_PAIR;
+  out8[7] = static_cast<int32_t>(sizeof(fmoe::MoeParams));
+  return 0;
+}
+int fmoe_spec_prepare(size_t smem) { return static_cast<int>(fmoe::moe_prepare_kernel(smem)); }
+int fmoe_spec_launch(const void* params, const void* maps, int grid, size_t smem, void* stream) {
+  return static_cast<int>(fmoe::launch_moe(*static_cast<const fmoe::MoeParams*>(params),
+                                           static_cast<const CUtensorMap*>(maps), grid, smem,
+                                           static_cast<cudaStream_t>(stream)));
+}
+}
+#endif

@@ -2,15 +2,31 @@
 
 The names, constructor arguments, defaults and enum values mirror the reference's
 flashmoe/jit.py:7-151 so that a script written against `flashmoe` runs against this package
-unchanged (`import flashmoe_b200 as flashmoe`).  Where the reference compiles one shared
-object per model description at `initialize` time (flashmoe/jit.py:153-296), this package
-ships one ahead-of-time library whose kernels take the shapes at run time; `_get_compiled`
-therefore only locates (and, if asked, builds) that library.
+unchanged (`import flashmoe_b200 as flashmoe`).
+
+The reference compiles one shared object per model description at `initialize` time
+(flashmoe/jit.py:153-296).  Here the ahead-of-time library (`_get_compiled`) already runs every
+description with the shapes as run-time arguments; on top of it `specialised_library` builds,
+per description, a small library holding the persistent kernel with H, I, top-k, the MLP type,
+the activation, the element type and the tile form as compile-time constants, under the
+reference's cache protocol: a key hashed from the description and the kernel sources, a lock file
+created with O_EXCL so that one process of a job builds while the others wait for the artefact,
+and an atomic rename to publish it.  `initialize` loads a specialised library when the cache holds
+one (or builds it when FMOE_JIT=1) and falls back to the generic kernel otherwise; both give the
+same bits.
 """
 from __future__ import annotations
 
+import hashlib
 import math
+import os
+import shutil
+import socket
+import subprocess
+import threading
+import time
 from enum import IntEnum
+from pathlib import Path
 from typing import List, Optional
 
 
@@ -134,3 +150,89 @@ def _get_compiled(arg: Optional[InitArgs] = None, src=None, mod_prefix: str = ""
     """
     from . import _native
     return _native.lib()
+
+
+# ---- per-description specialisation of the persistent kernel ------------------------------------
+
+SPEC_SOURCES = ("csrc/moe_kernel.cu", "csrc/common.cuh", "csrc/ptx.cuh", "../include/flashmoe_b200.h")
+SPEC_FLAGS = ("-std=c++17", "-O3", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo",
+              "-Xcompiler", "-fPIC", "-shared")
+
+
+def spec_cache_dir() -> Path:
+    """FLASHMOE_CACHE_DIR as in the reference (jit.py:199); the default is inside the package so
+    that libraries built ahead of time travel with it."""
+    return Path(os.environ.get("FLASHMOE_CACHE_DIR", str(Path(__file__).resolve().parent / "lib" / "spec")))
+
+
+def _source_fingerprint() -> str:
+    root = Path(__file__).resolve().parent
+    h = hashlib.sha256(b"flashmoe-b200-spec-v1")
+    for rel in SPEC_SOURCES:
+        path = (root / rel).resolve()
+        h.update(rel.encode())
+        h.update(path.read_bytes())
+    return h.hexdigest()[:16]
+
+
+def spec_defines(arg: "InitArgs", pair: bool) -> List[str]:
+    return [f"-DFMOE_SPEC=1", f"-DFMOE_SPEC_H={arg.token_dim}", f"-DFMOE_SPEC_I={arg.ffn_size}",
+            f"-DFMOE_SPEC_K={arg.top_k}", f"-DFMOE_SPEC_GATED={1 if arg.mlp_type == MLPType.GATED else 0}",
+            f"-DFMOE_SPEC_ACT={int(arg.act_type)}", f"-DFMOE_SPEC_DT={int(arg.data_type)}",
+            f"-DFMOE_SPEC_PAIR={1 if pair else 0}"]
+
+
+def spec_key(arg: "InitArgs", pair: bool) -> str:
+    text = "|".join(spec_defines(arg, pair) + list(SPEC_FLAGS) + [_source_fingerprint()])
+    return hashlib.sha256(text.encode()).hexdigest()[:16]
+
+
+def specialised_library(arg: "InitArgs", pair: bool = False, build: Optional[bool] = None,
+                        timeout_s: float = 600.0) -> Optional[Path]:
+    """Path of the kernel library specialised for `arg`, or None.
+
+    Cached under spec_cache_dir()/fmoe_spec_<key>.so.  A missing library is built when `build` is
+    true (default: the FMOE_JIT environment variable is "1"): the first process to create the lock
+    file compiles into a private temporary name and publishes it with an atomic rename; every other
+    process polls for the final name (flashmoe/jit.py:223-296 does the same around cmake)."""
+    cache = spec_cache_dir()
+    so_path = cache / f"fmoe_spec_{spec_key(arg, pair)}.so"
+    if so_path.exists():
+        return so_path
+    if build is None:
+        build = os.environ.get("FMOE_JIT", "0") == "1"
+    if not build:
+        return None
+    nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+    if not os.path.exists(nvcc):
+        return None
+    cache.mkdir(parents=True, exist_ok=True)
+    lock_path = so_path.with_suffix(".lock")
+    uniq = f"{socket.gethostname()}_pid{os.getpid()}_tid{threading.get_ident()}"
+    try:
+        fd = os.open(lock_path, os.O_CREAT | os.O_EXCL | os.O_WRONLY)
+        with os.fdopen(fd, "w") as f:
+            f.write(f"{uniq}\ntime={time.time()}\n")
+    except FileExistsError:
+        start = time.time()                      # somebody else is the builder: wait for the artefact
+        while not so_path.exists():
+            if time.time() - start > timeout_s:
+                raise TimeoutError(f"timed out waiting for {so_path} while another process was building it")
+            time.sleep(0.1)
+        return so_path
+    try:
+        if so_path.exists():                     # finished just before we took the lock
+            return so_path
+        src = Path(__file__).resolve().parent / "csrc" / "moe_kernel.cu"
+        tmp = cache / f".{so_path.stem}.{uniq}.tmp.so"
+        cmd = [nvcc, *SPEC_FLAGS, *spec_defines(arg, pair), "-o", str(tmp), str(src)]
+        proc = subprocess.run(cmd, cwd=src.parent, capture_output=True, text=True)
+        if proc.returncode != 0:
+            raise RuntimeError("nvcc failed building a specialised kernel:\n" + proc.stdout + proc.stderr)
+        tmp.replace(so_path)                     # atomic publish
+    finally:
+        try:
+            lock_path.unlink()
+        except FileNotFoundError:
+            pass
+    return so_path

@@ -157,6 +157,14 @@ int fmoe_ctx_destroy(fmoe_ctx* ctx, void* stream);
 #define FMOE_LAYER_CACHE 128
 int fmoe_forward(fmoe_ctx* ctx, const fmoe_forward_args* args, void* stream);
 
+/* Replaces the per-model JIT module of the reference (flashmoe/jit.py:188-296, bindings.py:34-46:
+ * shapes as constexpr): `path` is a shared library built from the same kernel source with the
+ * layer's H, I, top-k, MLP type, activation, element type and tile form fixed at compile time
+ * (flashmoe_b200.jit builds and caches them).  The library is checked against this context's
+ * description and refused if it differs; on success fmoe_forward launches the specialised kernel
+ * instead of the generic one.  Results are bit-identical either way. */
+int fmoe_ctx_load_specialised(fmoe_ctx* ctx, const char* path);
+
 /* No counterpart in the reference (its FP32 kernels read fp32 weights directly).  An FP32 context
  * runs the expert GEMMs on BF16 tensor cores with every weight held as three BF16 planes; it keeps
  * the planes of the weight set it saw last, keyed by the three weight addresses, so the split is
@@ -235,6 +243,8 @@ typedef struct fmoe_geometry {
   int32_t cta_pairs;       /* 1: tiles are worked by CTA pairs (cta_group::2), 0: by single CTAs */
   int32_t split_parts;     /* K parts per GEMM1 tile of the closing wave (1: no tile is cut) */
   int64_t symm_bytes, workspace_bytes;
+  int32_t specialised;     /* 1: forwards run a kernel compiled for this layer's description */
+  int32_t reserved;
 } fmoe_geometry;
 int fmoe_get_geometry(const fmoe_ctx* ctx, fmoe_geometry* out);
 

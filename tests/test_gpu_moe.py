@@ -92,6 +92,27 @@ def test_closing_gemm1_tiles_cut_along_k(name, parts, monkeypatch):
         layer.close()
 
 
+@pytest.mark.parametrize("name", ["bf16_gated_k2", "fp32_vanilla_gelu_k4"])
+def test_specialised_kernel_gives_the_generic_kernel_s_bits(name, monkeypatch):
+    """The kernel compiled for this layer's description (H, I, top-k, MLP type, activation and
+    element type as constants; built by flashmoe_b200.jit, cached in the package) against the
+    generic one that reads them from the launch parameters."""
+    w = GOLDEN_CASES[name]
+    lw, x = make_weights(w), make_tokens(w)
+    ref, _ = oracle_layer(w, x=x, lw=lw)
+    outs = {}
+    for mode in ("off", "1"):
+        monkeypatch.setenv("FMOE_JIT", mode)
+        layer = make_layer(w, lw)
+        try:
+            assert layer.geometry().specialised == (0 if mode == "off" else 1)
+            outs[mode] = layer.forward(x).cpu()
+            assert_close(outs[mode], ref, w.data_type, f"{name} FMOE_JIT={mode}")
+        finally:
+            layer.close()
+    assert torch.equal(outs["off"], outs["1"])
+
+
 def test_one_context_serves_several_layers():
     """Three layers of one model (same shapes, different weights) run through ONE context, in turn
     and repeatedly: every forward equals what a context of its own gives for that layer, bit for
