@@ -367,6 +367,22 @@ def short_measure(name, tokens, world, rank, local_rank, dev, dist, peaks, peaks
         fwd_us = mx(statistics.mean(e[1].elapsed_time(e[2]) for e in ev) * 1e3)
         phases = layer.phases()
         counts = layer.counts.cpu().numpy()
+        # decode-sized batches: the same step as ONE launch (the router as the kernel's first phase)
+        one_launch_us = None
+        if w.tokens_per_rank <= 128:
+            with torch.cuda.stream(st):
+                for _ in range(3):
+                    layer.step_one_launch()
+            sync()
+            o0, o1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            with torch.cuda.stream(st):
+                o0.record(st)
+                for _ in range(steps):
+                    layer.step_one_launch()
+                o1.record(st)
+            sync()
+            layer.check()
+            one_launch_us = mx(o0.elapsed_time(o1) / steps * 1e3)
         if world > 1:
             allc = [None] * world
             dist.all_gather_object(allc, counts.tolist())
@@ -379,7 +395,7 @@ def short_measure(name, tokens, world, rank, local_rank, dev, dist, peaks, peaks
             oks = [None] * world
             dist.all_gather_object(oks, par["ok"])
         res = {"workload": f"{name}@{w.tokens_per_rank}", "dtype": w.data_type.name.lower(),
-               "fwd_us": fwd_us, "router_us": router_us,
+               "fwd_us": fwd_us, "router_us": router_us, "step_as_one_launch_us": one_launch_us,
                "tokens_per_s": w.tokens_per_rank * world / ((fwd_us + router_us) * 1e-6),
                "bound": roof["bound"], "frac": roof["frac"],
                "pct_dense_bf16_peak_burst": roof["pct_dense_bf16_peak_burst"],

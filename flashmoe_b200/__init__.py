@@ -71,6 +71,14 @@ class _MoEModule:
                            local_bias_down or None, moe_out, swish_alpha, swish_beta)
         N.check(self._lib.fmoe_forward(C.c_void_p(raw_ctx), C.byref(a), C.c_void_p(stream_ptr)), "forward")
 
+    def forward_routed(self, raw_ctx, rargs: "router.RouterForwardArgs", fargs: ForwardArgs) -> None:
+        ra = N.RouterArgsC(0, rargs.weights, rargs.routing or None, rargs.expert_counts, rargs.logit_bias or None)
+        fa = N.ForwardArgsC(fargs.tokens, fargs.expert_counts, fargs.local_expert_up, fargs.local_expert_up_v or None,
+                            fargs.local_bias_up or None, fargs.local_bias_up_v or None, fargs.local_expert_down,
+                            fargs.local_bias_down or None, fargs.moe_out, fargs.swish_alpha, fargs.swish_beta)
+        N.check(self._lib.fmoe_forward_routed(C.c_void_p(raw_ctx), C.byref(ra), C.byref(fa),
+                                              C.c_void_p(fargs.stream_ptr)), "forward (routed)")
+
     def get_tIdx(self, raw_ctx) -> int:
         out = C.c_void_p()
         N.check(self._lib.fmoe_token_indices(C.c_void_p(raw_ctx), C.byref(out)), "get_tIdx")
@@ -161,8 +169,14 @@ def get_workspace_bytes(arg: InitArgs, ep_world: int = None, num_local_experts: 
     return {"symmetric": symm.value, "workspace": work.value}
 
 
-def forward(handle: ContextHandle, args: ForwardArgs) -> None:
-    """One launch of the fused dispatch + experts + combine kernel on `args.stream_ptr`."""
+def forward(handle: ContextHandle, args: ForwardArgs, router_args: "router.RouterForwardArgs" = None) -> None:
+    """One launch of the fused dispatch + experts + combine kernel on `args.stream_ptr`.
+
+    With `router_args` the same launch opens with the router (an addition of this package: no
+    `router.forward` call is needed for that step; `router_args.tokens` is ignored)."""
+    if router_args is not None:
+        handle.mod.forward_routed(handle.context, router_args, args)
+        return
     handle.mod.forward(handle.context, tokens=args.tokens, expert_counts=args.expert_counts,
                        local_expert_up=args.local_expert_up, local_expert_up_v=args.local_expert_up_v,
                        local_bias_up=args.local_bias_up, local_bias_up_v=args.local_bias_up_v,

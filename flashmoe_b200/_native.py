@@ -75,6 +75,7 @@ SIGNATURES = {
     "fmoe_token_indices": (C.c_int, [C.c_void_p, C.POINTER(C.c_void_p)]),
     "fmoe_ctx_destroy": (C.c_int, [C.c_void_p, C.c_void_p]),
     "fmoe_forward": (C.c_int, [C.c_void_p, C.POINTER(ForwardArgsC), C.c_void_p]),
+    "fmoe_forward_routed": (C.c_int, [C.c_void_p, C.POINTER(RouterArgsC), C.POINTER(ForwardArgsC), C.c_void_p]),
     "fmoe_weights_changed": (C.c_int, [C.c_void_p]),
     "fmoe_ctx_load_specialised": (C.c_int, [C.c_void_p, C.c_char_p]),
     "fmoe_router_create": (C.c_int, [C.POINTER(ModelDesc), C.c_int32, C.c_int32, C.c_void_p,

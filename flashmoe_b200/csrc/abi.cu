@@ -433,6 +433,7 @@ int fmoe_ctx_create(const fmoe_model_desc* model, const fmoe_ep_desc* ep, void* 
   p.done_ctas = reinterpret_cast<uint32_t*>(c->work + w_ctl + 64);
   p.abort_word = reinterpret_cast<uint32_t*>(c->work + w_ctl + 128);
   p.epoch = reinterpret_cast<uint64_t*>(c->work + w_ctl + 192);
+  p.grid_bar = reinterpret_cast<unsigned long long*>(c->work + w_ctl + 208);
   p.status = reinterpret_cast<fmoe_status*>(c->work + w_status);
   p.trace = reinterpret_cast<unsigned long long*>(c->work + w_trace);
   p.table = reinterpret_cast<const TokenSlot*>(c->work + w_table);
@@ -550,14 +551,32 @@ int fmoe_ctx_destroy(fmoe_ctx* ctx, void* stream) {
   return FMOE_OK;
 }
 
+static int forward_impl(fmoe_ctx* ctx, const fmoe_forward_args* a, const fmoe_router_args* ra, void* stream);
+
 int fmoe_forward(fmoe_ctx* ctx, const fmoe_forward_args* a, void* stream) {
+  return forward_impl(ctx, a, nullptr, stream);
+}
+
+int fmoe_forward_routed(fmoe_ctx* ctx, const fmoe_router_args* ra, const fmoe_forward_args* a, void* stream) {
+  if (ra == nullptr) return set_error(FMOE_ERR_INVALID_ARG, "null argument");
+  if (ra->weights == nullptr || ra->expert_counts == nullptr)
+    return set_error(FMOE_ERR_INVALID_ARG, "weights and expert_counts are required");
+  if (reinterpret_cast<uintptr_t>(ra->weights) & 15)
+    return set_error(FMOE_ERR_INVALID_ARG, "the router weights must be 16-byte aligned");
+  if ((reinterpret_cast<uintptr_t>(ra->expert_counts) | reinterpret_cast<uintptr_t>(ra->routing) |
+       reinterpret_cast<uintptr_t>(ra->logit_bias)) & 3)
+    return set_error(FMOE_ERR_INVALID_ARG, "expert_counts, routing and logit_bias must be 4-byte aligned");
+  return forward_impl(ctx, a, ra, stream);
+}
+
+static int forward_impl(fmoe_ctx* ctx, const fmoe_forward_args* a, const fmoe_router_args* ra, void* stream) {
   if (ctx == nullptr || a == nullptr) return set_error(FMOE_ERR_INVALID_ARG, "null argument");
   if (!ctx->committed) return set_error(FMOE_ERR_NOT_READY, "call fmoe_ctx_commit after importing every peer");
   if (ctx->poisoned)
     return set_error(FMOE_ERR_DEVICE_TIMEOUT, "an earlier forward of this context ran out of a device-side wait "
                                               "(see fmoe_last_status); destroy the context and create a new one");
   const bool gated = ctx->params.gated != 0;
-  if (a->tokens == nullptr || a->expert_counts == nullptr || a->local_expert_up == nullptr ||
+  if (a->tokens == nullptr || (ra == nullptr && a->expert_counts == nullptr) || a->local_expert_up == nullptr ||
       a->local_expert_down == nullptr || a->moe_out == nullptr || (gated && a->local_expert_up_v == nullptr))
     return set_error(FMOE_ERR_INVALID_ARG, "a required device pointer is null");
   if ((reinterpret_cast<uintptr_t>(a->tokens) | reinterpret_cast<uintptr_t>(a->moe_out) |
@@ -603,6 +622,10 @@ int fmoe_forward(fmoe_ctx* ctx, const fmoe_forward_args* a, void* stream) {
     ctx->maps[2] = hit->m[0]; ctx->maps[3] = hit->m[1]; ctx->maps[4] = hit->m[2];
   }
   p.tokens = a->tokens; p.expert_counts = a->expert_counts;
+  if (ra != nullptr) {   // the router runs as the first phase of this launch
+    p.router_w = ra->weights; p.logit_bias = ra->logit_bias; p.routing = ra->routing;
+    p.counts_out = ra->expert_counts; p.expert_counts = ra->expert_counts;
+  }
   p.bias_up = a->local_bias_up; p.bias_up_v = a->local_bias_up_v; p.bias_down = a->local_bias_down;
   p.out = a->moe_out; p.alpha = a->swish_alpha; p.beta = a->swish_beta;
   if (ctx->spec_launch != nullptr) {

@@ -87,6 +87,15 @@ struct MoeParams {
   const TokenSlot* table;  // [E][round_ec]
   const Route* routes;     // [S][k]
 
+  // Routing inside this launch (fmoe_forward_routed): non-null router_w makes the kernel open with
+  // the router itself (logits, softmax, top-k, slots; same arithmetic as the router kernels) and
+  // write expert_counts, the routing table and the route records before it exchanges counts.
+  const void* router_w;     // [E, H] Element, or null: the router ran as launches of its own
+  const float* logit_bias;  // [E] or null
+  float* routing;           // [S, E] probabilities out, or null
+  int32_t* counts_out;      // [E] (the same array as expert_counts)
+  unsigned long long* grid_bar;   // arrivals at the routing phase's grid barriers (zero between launches)
+
   // per forward
   const void* tokens;
   const int32_t* expert_counts;

@@ -45,6 +45,7 @@
 
 #include "common.cuh"
 #include "ptx.cuh"
+#include "router_math.cuh"
 
 namespace fmoe {
 
@@ -347,6 +348,118 @@ __device__ __forceinline__ void moe_forward_body(const MoeParams& p, const TmaMa
   const uint64_t epoch = ctl->epoch;
   const uint64_t flag_val = epoch + 1;
   const int parity = static_cast<int>(epoch & 1);
+
+  // ---- routing inside the launch (optional) ----------------------------------------------
+  // The router's two steps as phases of this kernel, for callers that want one launch per
+  // layer (decode-sized batches, where two extra launches cost as much as the layer): every warp
+  // of the grid takes tokens and runs logits, softmax and top-k in the router kernels' own fp32
+  // order (lane l of the warp owns the 8-element vectors v = l mod 32 of H, ascending, one FMA per
+  // element; xor-butterfly fold), a grid barrier, every CTA takes experts and hands out slots in
+  // ascending token order, a second barrier.  The stage ring is idle until the first ticket and
+  // lends each warp a row of E floats.
+  if (p.router_w != nullptr) {
+    auto grid_barrier = [&](unsigned long long target) {
+      __syncthreads();
+      if (tid == 0) {
+        __threadfence();
+        atomicAdd(p.grid_bar, 1ull);
+        SpinGuard g;
+        while (ld_acquire_gpu(reinterpret_cast<const uint64_t*>(p.grid_bar)) < target) {
+          if (g.expired(wc)) {
+            if (ld_acquire_gpu(reinterpret_cast<const uint64_t*>(p.grid_bar)) < target) { fail(p, FMOE_PHASE_ROUTING, target); ctl->ok = 0; }
+            break;
+          }
+        }
+      }
+      __syncthreads();
+    };
+    {
+      const T* __restrict__ X = static_cast<const T*>(p.tokens);
+      const T* __restrict__ Wr = static_cast<const T*>(p.router_w);
+      float* row = reinterpret_cast<float*>(stages) + static_cast<size_t>(warp) * E;
+      const int nvec = H_ >> 3, iters = (nvec + 31) >> 5;
+      Route* routes = const_cast<Route*>(p.routes);
+      for (int tok = blockIdx.x * (kThreads / 32) + warp; tok < p.S; tok += gridDim.x * (kThreads / 32)) {
+        for (int eg = 0; eg < E; eg += 8) {
+          float acc[8];
+#pragma unroll
+          for (int e = 0; e < 8; ++e) acc[e] = 0.0f;
+          for (int it = 0; it < iters; ++it) {
+            const int v = it * 32 + lane;
+            if (v < nvec) {
+              float xv[8];
+              Vec8<T>::load(X + static_cast<size_t>(tok) * H_ + v * 8, xv);
+#pragma unroll
+              for (int e = 0; e < 8; ++e) {
+                float wv[8];
+                Vec8<T>::load(Wr + static_cast<size_t>(eg + e) * H_ + v * 8, wv);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                  if constexpr (Vec8<T>::kExactProducts) acc[e] = __fmaf_rn(xv[j], wv[j], acc[e]);
+                  else acc[e] = __fadd_rn(acc[e], __fmul_rn(xv[j], wv[j]));
+                }
+              }
+            }
+          }
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            const int ex = eg + e;
+            const float sum = butterfly_sum(acc[e]);
+            if (lane == (ex & 31)) row[ex] = p.logit_bias ? __fadd_rn(sum, __ldg(p.logit_bias + ex)) : sum;
+          }
+        }
+        __syncwarp();
+        int idx;
+        float weight;
+        softmax_topk_row(E, K_, p.routing, row, tok, lane, idx, weight);
+        if (lane < K_) routes[static_cast<size_t>(tok) * K_ + lane] = Route{idx, 0x7fffffff, weight, 0};
+        __syncwarp();
+      }
+    }
+    grid_barrier(gridDim.x);
+    if (ctl->ok) {
+      // slots: one CTA per expert (strided), tokens in ascending order, kThreads at a time
+      int* warp_tot = reinterpret_cast<int*>(stages);      // [warps] + running base
+      Route* routes = const_cast<Route*>(p.routes);
+      TokenSlot* table = const_cast<TokenSlot*>(p.table);
+      for (int e = blockIdx.x; e < E; e += gridDim.x) {
+        __syncthreads();
+        if (tid == 0) warp_tot[8] = 0;
+        __syncthreads();
+        for (int c0 = 0; c0 < p.S; c0 += kThreads) {
+          const int tkn = c0 + tid;
+          int hit = -1;
+          if (tkn < p.S) {
+            for (int j = 0; j < K_; ++j)
+              if (__ldcg(&routes[static_cast<size_t>(tkn) * K_ + j].expert) == e) { hit = j; break; }
+          }
+          const unsigned ballot = __ballot_sync(0xffffffffu, hit >= 0);
+          const int before = __popc(ballot & ((1u << lane) - 1));
+          if (lane == 0) warp_tot[warp] = __popc(ballot);
+          __syncthreads();
+          int warp_base = 0, total = 0;
+          for (int w = 0; w < kThreads / 32; ++w) {
+            const int c = warp_tot[w];
+            if (w < warp) warp_base += c;
+            total += c;
+          }
+          const int base = warp_tot[8];
+          if (hit >= 0) {
+            const int slot = base + warp_base + before;
+            Route* rt = &routes[static_cast<size_t>(tkn) * K_ + hit];
+            const float wt = __ldcg(&rt->weight);
+            if (slot < p.EC) table[static_cast<size_t>(e) * p.round_ec + slot] = TokenSlot{static_cast<uint32_t>(tkn), wt};
+            rt->slot = slot;
+          }
+          __syncthreads();
+          if (tid == 0) warp_tot[8] = base + total;
+          __syncthreads();
+        }
+        if (tid == 0) p.counts_out[e] = warp_tot[8];
+      }
+    }
+    grid_barrier(2ull * gridDim.x);
+  }
 
   // ---- count exchange (CTA 0 publishes; everyone waits) --------------------------------
   if (blockIdx.x == 0) {
@@ -1202,6 +1315,7 @@ __device__ __forceinline__ void moe_forward_body(const MoeParams& p, const TmaMa
     const uint32_t prev = atomicAdd(p.done_ctas, 1u);
     if (prev == gridDim.x - 1) {
       *p.done_ctas = 0;
+      *p.grid_bar = 0ull;
       *p.epoch = epoch + 1;
       p.status->epoch = epoch + 1;
     }

@@ -23,79 +23,11 @@
 #include <mutex>
 
 #include "common.cuh"
+#include "router_math.cuh"
 
 namespace fmoe {
 
 namespace {
-
-
-// 2^f on [-0.5, 0.5]: (ln 2)^k / k!, k = 0..7, rounded to fp32.
-__device__ __forceinline__ float det_exp(float x) {
-  float t = __fmul_rn(x, 0x1.715476p+0f);
-  t = fmaxf(t, -100.0f);
-  const float n = rintf(t);
-  const float f = __fsub_rn(t, n);
-  float p = 0x1.ffcbfcp-17f;
-  p = __fadd_rn(__fmul_rn(p, f), 0x1.430912p-13f);
-  p = __fadd_rn(__fmul_rn(p, f), 0x1.5d87fep-10f);
-  p = __fadd_rn(__fmul_rn(p, f), 0x1.3b2ab6p-7f);
-  p = __fadd_rn(__fmul_rn(p, f), 0x1.c6b08ep-5f);
-  p = __fadd_rn(__fmul_rn(p, f), 0x1.ebfbep-3f);
-  p = __fadd_rn(__fmul_rn(p, f), 0x1.62e43p-1f);
-  p = __fadd_rn(__fmul_rn(p, f), 1.0f);
-  const float scale = __int_as_float((static_cast<int>(n) + 127) << 23);
-  return __fmul_rn(p, scale);
-}
-
-__device__ __forceinline__ float butterfly_sum(float v) {
-#pragma unroll
-  for (int off = 16; off >= 1; off >>= 1) v = __fadd_rn(v, __shfl_xor_sync(0xffffffffu, v, off));
-  return v;
-}
-
-template <typename T>
-struct Vec8;  // loads 8 consecutive elements as fp32
-
-template <>
-struct Vec8<__nv_bfloat16> {
-  static constexpr bool kExactProducts = true;
-  static constexpr bool kIsBf16 = true;
-  __device__ __forceinline__ static void load(const void* p, float (&f)[8]) {
-    const uint4 u = __ldg(reinterpret_cast<const uint4*>(p));
-    const uint32_t w[4] = {u.x, u.y, u.z, u.w};
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      f[2 * i] = __uint_as_float(w[i] << 16);
-      f[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
-    }
-  }
-};
-template <>
-struct Vec8<__half> {
-  static constexpr bool kExactProducts = true;
-  static constexpr bool kIsBf16 = false;
-  __device__ __forceinline__ static void load(const void* p, float (&f)[8]) {
-    const uint4 u = __ldg(reinterpret_cast<const uint4*>(p));
-    const uint32_t w[4] = {u.x, u.y, u.z, u.w};
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const float2 v = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
-      f[2 * i] = v.x;
-      f[2 * i + 1] = v.y;
-    }
-  }
-};
-template <>
-struct Vec8<float> {
-  static constexpr bool kExactProducts = false;
-  static constexpr bool kIsBf16 = false;
-  __device__ __forceinline__ static void load(const void* p, float (&f)[8]) {
-    const float4 a = __ldg(reinterpret_cast<const float4*>(p));
-    const float4 b = __ldg(reinterpret_cast<const float4*>(p) + 1);
-    f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w;
-    f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
-  }
-};
 
 // 8 consecutive elements as loaded (16 or 32 bytes), converted to fp32 only when they are used, so
 // that a load issued several iterations ahead does not stall the warp where it is issued.
@@ -331,49 +263,153 @@ router_topk_kernel(const RouterParams p) {
   for (int t = part; t < TT; t += ES) {   // the parts share the group's tokens for the softmax
     const int tok = t0 + t;
     if (tok >= p.S) break;
-    float* r = rows + t * E;
-    float m = -INFINITY;
-    for (int j = lane; j < E; j += 32) m = fmaxf(m, r[j]);
+    softmax_topk_row(p, rows + t * E, tok, lane);
+  }
+}
+
+// ---- many experts (E a multiple of 32, E >= 64) --------------------------------------------
+// Same arithmetic, operation for operation, as router_topk_kernel; what differs is how the
+// operands reach the FMA pipe.  Per 256-element chunk of H the CTA converts the 32 x 256 weight
+// chunk to fp32 ONCE (not per warp and per use) and parks it in shared memory as
+// [element j][expert quad][lane][4 experts], so that a lane fetches four experts' weights for its
+// own 8-element vector with one conflict-free 16-byte load; the raw chunk for the next step is
+// already in registers while this one is consumed.  The multiply-adds are issued two at a time
+// (fma.rn.f32x2: two independent fp32 FMAs per instruction, each rounded as a scalar FMA would
+// be), one pair = one token against two neighbouring experts, so every accumulator still sees its
+// products in the same order and the result bits are unchanged.
+__device__ __forceinline__ unsigned long long pack2(float lo, float hi) {
+  unsigned long long r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void unpack2(unsigned long long v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ unsigned long long fma2(unsigned long long a, unsigned long long b, unsigned long long c) {
+  unsigned long long d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+template <typename T, int TT>
+__global__ void __launch_bounds__(512)
+router_topk_wide_kernel(const RouterParams p) {
+  constexpr int EG = 32, TG = 4, ES = 4, EP = EG / ES;   // 16 warps, 8 experts per warp
+  constexpr int kStageFloats = 8 * EG * 32;                                // one chunk: 32 KB
+  extern __shared__ __align__(16) unsigned char s_raw[];
+  float* s_row = reinterpret_cast<float*>(s_raw);  // [TG][TT][E]: logits, then exp, then probabilities
+  const int H = p.H, E = p.E;
+  float4* wst = reinterpret_cast<float4*>(s_raw + ((static_cast<size_t>(TG) * TT * E * sizeof(float) + 15) & ~size_t(15)));
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tg = warp % TG, part = warp / TG;
+  const int t0 = (blockIdx.x * TG + tg) * TT;
+  const int nvec = H >> 3;
+  const int iters = (nvec + 31) >> 5;
+  const T* __restrict__ X = static_cast<const T*>(p.tokens);
+  const T* __restrict__ Wr = static_cast<const T*>(p.weights);
+  float* rows = s_row + static_cast<size_t>(tg) * TT * E;
+
+  // staging: warps 0..7, warp w = expert quad w of the group, lane = vector of the chunk
+  const bool stager = warp < EG / 4;
+  Raw8<T> wraw[4];
+  auto fetch_w = [&](int eg, int it) {
+    const int v = it * 32 + lane;
+    if (stager && it < iters && v < nvec) {
 #pragma unroll
-    for (int off = 16; off >= 1; off >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, off));
-    float d = 0.0f;
-    for (int j = lane; j < E; j += 32) {
-      const float ex = det_exp(__fsub_rn(r[j], m));
-      r[j] = ex;
-      d = __fadd_rn(d, ex);
+      for (int q = 0; q < 4; ++q) wraw[q].fetch(Wr + static_cast<size_t>(eg + warp * 4 + q) * H + v * 8);
     }
-    d = butterfly_sum(d);
-    for (int j = lane; j < E; j += 32) {
-      const float pr = __fdiv_rn(r[j], d);
-      r[j] = pr;
-      if (p.routing) p.routing[static_cast<size_t>(tok) * E + j] = pr;
-    }
-    float wsum = 0.0f, my_p = 0.0f;
-    int my_idx = 0;
-    for (int round = 0; round < p.k; ++round) {
-      float bv = -INFINITY;
-      int bi = 0x7fffffff;
-      for (int j = lane; j < E; j += 32) {
-        const float v = r[j];
-        if (v > bv) { bv = v; bi = j; }
-      }
+  };
+  auto park_w = [&](int it) {
+    const int v = it * 32 + lane;
+    if (stager && it < iters && v < nvec) {
+      float f[4][8];
 #pragma unroll
-      for (int off = 16; off >= 1; off >>= 1) {
-        const float ov = __shfl_xor_sync(0xffffffffu, bv, off);
-        const int oi = __shfl_xor_sync(0xffffffffu, bi, off);
-        if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+      for (int q = 0; q < 4; ++q) wraw[q].unpack(f[q]);
+      float4* dst = wst + static_cast<size_t>(it & 1) * (kStageFloats / 4) + warp * 32 + lane;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) dst[j * (EG / 4) * 32] = make_float4(f[0][j], f[1][j], f[2][j], f[3][j]);
+    }
+  };
+
+  for (int eg = 0; eg < E; eg += EG) {
+    unsigned long long acc[TT][EP / 2];
+#pragma unroll
+    for (int t = 0; t < TT; ++t)
+#pragma unroll
+      for (int e = 0; e < EP / 2; ++e) acc[t][e] = 0ull;
+
+    Raw8<T> xr[TT];
+    auto fetch_x = [&](int it) {
+      const int v = it * 32 + lane;
+      if (it < iters && v < nvec) {
+#pragma unroll
+        for (int t = 0; t < TT; ++t) {
+          const int tok = min(t0 + t, p.S - 1);  // ragged last group: recompute the last token
+          xr[t].fetch(X + static_cast<size_t>(tok) * H + v * 8);
+        }
       }
-      if (bi == 0x7fffffff) bi = 0;  // nothing left to pick (all NaN)
-      if (lane == (bi & 31)) r[bi] = -INFINITY;
-      wsum = __fadd_rn(wsum, bv);
-      if (lane == (round & 31)) { my_p = bv; my_idx = bi; }
-      __syncwarp();
+    };
+    __syncthreads();            // the previous group's last chunk has been read by every warp
+    fetch_w(eg, 0);
+    fetch_x(0);
+    park_w(0);
+    __syncthreads();
+    for (int it = 0; it < iters; ++it) {
+      fetch_w(eg, it + 1);      // in flight while this chunk is consumed
+      if (it * 32 + lane < nvec) {
+        float xv[TT][8];
+#pragma unroll
+        for (int t = 0; t < TT; ++t) xr[t].unpack(xv[t]);
+        fetch_x(it + 1);
+        const float4* wb = wst + static_cast<size_t>(it & 1) * (kStageFloats / 4) + (part * 2) * 32 + lane;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const float4 wa = wb[j * (EG / 4) * 32], wc = wb[j * (EG / 4) * 32 + 32];
+          const unsigned long long wp[4] = {pack2(wa.x, wa.y), pack2(wa.z, wa.w), pack2(wc.x, wc.y), pack2(wc.z, wc.w)};
+#pragma unroll
+          for (int t = 0; t < TT; ++t) {
+            const unsigned long long xx = pack2(xv[t][j], xv[t][j]);
+#pragma unroll
+            for (int e = 0; e < EP / 2; ++e) {
+              if constexpr (Vec8<T>::kExactProducts) {
+                acc[t][e] = fma2(xx, wp[e], acc[t][e]);
+              } else {
+                // fp32 inputs: a rounded multiply, then a rounded add, as scalar operations (the
+                // paired forms did not reproduce the scalar bits on sm_100a)
+                float a0, a1, w0, w1;
+                unpack2(acc[t][e], a0, a1);
+                unpack2(wp[e], w0, w1);
+                acc[t][e] = pack2(__fadd_rn(a0, __fmul_rn(xv[t][j], w0)), __fadd_rn(a1, __fmul_rn(xv[t][j], w1)));
+              }
+            }
+          }
+        }
+      } else {
+        fetch_x(it + 1);
+      }
+      park_w(it + 1);           // into the buffer chunk it - 1 left behind the last barrier
+      __syncthreads();
     }
-    if (lane < p.k) {
-      p.topk_idx[static_cast<size_t>(tok) * p.k + lane] = my_idx;
-      p.topk_w[static_cast<size_t>(tok) * p.k + lane] = __fdiv_rn(my_p, wsum);
+#pragma unroll
+    for (int t = 0; t < TT; ++t) {
+#pragma unroll
+      for (int e = 0; e < EP; ++e) {
+        float lo, hi;
+        unpack2(acc[t][e >> 1], lo, hi);
+        const int ex = eg + part * EP + e;
+        const float s = butterfly_sum((e & 1) ? hi : lo);
+        if (lane == (ex & 31)) {
+          const float b = p.logit_bias ? __ldg(p.logit_bias + ex) : 0.0f;
+          rows[t * E + ex] = p.logit_bias ? __fadd_rn(s, b) : s;
+        }
+      }
     }
-    __syncwarp();
+  }
+  __syncthreads();   // a token's logits come from all ES parts
+  if (t0 >= p.S) return;
+  for (int t = part; t < TT; t += ES) {   // the parts share the group's tokens for the softmax
+    const int tok = t0 + t;
+    if (tok >= p.S) break;
+    softmax_topk_row(p, rows + t * E, tok, lane);
   }
 }
 
@@ -443,8 +479,28 @@ cudaError_t launch_topk_eg(const RouterParams& p, cudaStream_t stream) {
 // two tokens per warp and the experts split over two warps measured fastest from 1 K to 8 K tokens
 // (Scout shapes, 1024 tokens: 21.5 us for both router kernels, against 24-43 us for the other
 // splits).
+template <typename T, int TT>
+cudaError_t launch_topk_wide(const RouterParams& p, cudaStream_t stream) {
+  const int ctas = (p.S + 4 * TT - 1) / (4 * TT);
+  const size_t rows = (static_cast<size_t>(4) * TT * p.E * sizeof(float) + 15) & ~size_t(15);
+  const size_t smem = rows + 2 * static_cast<size_t>(8 * 32 * 32) * sizeof(float);
+  cudaError_t e = cudaFuncSetAttribute(router_topk_wide_kernel<T, TT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       static_cast<int>(smem));
+  if (e != cudaSuccess) return e;
+  router_topk_wide_kernel<T, TT><<<ctas, 512, smem, stream>>>(p);
+  ++g_launches;
+  return cudaGetLastError();
+}
+
 template <typename T>
 cudaError_t launch_topk(const RouterParams& p, cudaStream_t stream) {
+  if (p.E >= 64 && p.E % 32 == 0) {
+    // with many experts: weights converted once per CTA, paired FMAs (router_topk_wide_kernel);
+    // TT = the most tokens per warp that still fills the SMs with warps
+    if (p.S >= 120 * 16) return launch_topk_wide<T, 4>(p, stream);
+    if (p.S >= 120 * 8) return launch_topk_wide<T, 2>(p, stream);
+    return launch_topk_wide<T, 1>(p, stream);
+  }
   if (p.E >= 64) {
     if (p.S >= 120 * 16) return launch_topk_eg<T, 4, 4, 4>(p, stream);
     if (p.S >= 120 * 8) return launch_topk_eg<T, 2, 4, 4>(p, stream);

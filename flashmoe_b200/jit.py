@@ -154,7 +154,8 @@ def _get_compiled(arg: Optional[InitArgs] = None, src=None, mod_prefix: str = ""
 
 # ---- per-description specialisation of the persistent kernel ------------------------------------
 
-SPEC_SOURCES = ("csrc/moe_kernel.cu", "csrc/common.cuh", "csrc/ptx.cuh", "../include/flashmoe_b200.h")
+SPEC_SOURCES = ("csrc/moe_kernel.cu", "csrc/common.cuh", "csrc/ptx.cuh", "csrc/router_math.cuh",
+                "../include/flashmoe_b200.h")
 SPEC_FLAGS = ("-std=c++17", "-O3", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo",
               "-Xcompiler", "-fPIC", "-shared")
 

@@ -107,6 +107,10 @@ class MoELayer:
         self.route()
         self.experts()
 
+    def step_one_launch(self) -> None:
+        """Router and experts as ONE launch (the router runs as the kernel's first phase)."""
+        flashmoe.forward(self.handle, self.fargs, router_args=self.rargs)
+
     def forward(self, tokens: torch.Tensor) -> torch.Tensor:
         """tokens [S, H] (any device) -> moe_out [S, H] on this layer's device (a fresh copy)."""
         with torch.cuda.stream(self.stream):

@@ -106,7 +106,7 @@ enum {
   FMOE_PHASE_NONE = 0, FMOE_PHASE_COUNTS = 1, FMOE_PHASE_DISPATCH_ARRIVAL = 2,
   FMOE_PHASE_GEMM0_DONE = 3, FMOE_PHASE_RETURN_ARRIVAL = 4, FMOE_PHASE_PIPE_FULL = 5,
   FMOE_PHASE_PIPE_EMPTY = 6, FMOE_PHASE_TMEM_FULL = 7, FMOE_PHASE_TMEM_EMPTY = 8,
-  FMOE_PHASE_TASK = 9
+  FMOE_PHASE_TASK = 9, FMOE_PHASE_ROUTING = 10
 };
 
 /* --- context life cycle -------------------------------------------------------------- */
@@ -156,6 +156,18 @@ int fmoe_ctx_destroy(fmoe_ctx* ctx, void* stream);
  * per layer, each with its own symmetric heap). */
 #define FMOE_LAYER_CACHE 128
 int fmoe_forward(fmoe_ctx* ctx, const fmoe_forward_args* args, void* stream);
+
+/* The reference's fused gate is a launch of its own and leaves "emit the top-k indices ... and fuse
+ * with the consumer" as a note (gate.cuh:554).  Here the consumer can take the router in: ONE launch
+ * that opens with the router (logits, softmax, top-k, slots, routing table: the arithmetic of
+ * fmoe_router_forward, bit for bit, run by the persistent kernel's own warps with two grid
+ * barriers) and goes on with dispatch, experts and combine.  `rargs->tokens` is ignored
+ * (`args->tokens` are routed); `rargs->expert_counts` is written and `args->expert_counts` ignored;
+ * `rargs->routing` ([S, E] probabilities) is written when non-null.  Meant for decode-sized
+ * batches, where two extra launches cost as much as the layer; for large batches the router
+ * kernels, which fill the SMs with many more warps, are faster. */
+int fmoe_forward_routed(fmoe_ctx* ctx, const fmoe_router_args* rargs, const fmoe_forward_args* args,
+                        void* stream);
 
 /* Replaces the per-model JIT module of the reference (flashmoe/jit.py:188-296, bindings.py:34-46:
  * shapes as constexpr): `path` is a shared library built from the same kernel source with the

@@ -113,6 +113,60 @@ def test_specialised_kernel_gives_the_generic_kernel_s_bits(name, monkeypatch):
     assert torch.equal(outs["off"], outs["1"])
 
 
+@pytest.mark.parametrize("name", ["bf16_gated_k2", "bf16_drop", "bf16_vanilla_gelu_k8", "fp32_gated_k2",
+                                  "fp16_gated_relu", "bf16_two_mtiles"])
+def test_router_inside_the_launch_gives_the_same_bits(name):
+    """fmoe_forward_routed: ONE launch whose first phase is the router.  Counts, route records,
+    probabilities and the layer's output must equal, bit for bit, what router.forward followed by
+    forward gives; repeated launches and new tokens included."""
+    w = GOLDEN_CASES[name]
+    lw = make_weights(w)
+    S, E, k = w.tokens_per_rank, w.num_experts, w.top_k
+    from flashmoe_b200.layer import MoELayer
+    layer = MoELayer(w, lw, return_logits=True)
+    try:
+        for step in range(3):
+            x = make_tokens(w.scaled(seed=w.seed + step))
+            layer.tokens.copy_(x)
+            torch.cuda.synchronize()
+            layer.step()
+            layer.check()
+            want = (layer.out.clone(), layer.counts.clone(), layer.routing.clone(),
+                    layer.debug(4, torch.int32, (S, k, 4))[:, :, :3].clone())
+            layer.out.zero_(); layer.counts.zero_(); layer.routing.zero_()
+            before = _launches()
+            layer.step_one_launch()
+            layer.check()
+            assert _launches() - before == 1
+            got = (layer.out, layer.counts, layer.routing, layer.debug(4, torch.int32, (S, k, 4))[:, :, :3])
+            assert torch.equal(got[1], want[1]), "counts"
+            assert torch.equal(got[3], want[3]), "route records"
+            assert torch.equal(got[2].view(torch.int32), want[2].view(torch.int32)), "probabilities"
+            assert torch.equal(got[0].view(torch.uint8), want[0].view(torch.uint8)), "output"
+        ref, _ = oracle_layer(w, x=x, lw=lw)
+        assert_close(layer.out.cpu(), ref, w.data_type, f"{name} routed in the launch")
+    finally:
+        layer.close()
+
+
+def test_router_inside_the_launch_at_decode_sizes():
+    """Qwen3 shapes with 1 and 16 tokens: the case the one-launch form is for."""
+    for S in (1, 16):
+        w = CONFIGS["qwen3"].scaled(tokens_per_rank=S)
+        lw, x = make_weights(w), make_tokens(w)
+        ref, _ = oracle_layer(w, x=x, lw=lw)
+        layer = make_layer(w, lw)
+        try:
+            layer.tokens.copy_(x)
+            torch.cuda.synchronize()
+            for _ in range(2):
+                layer.step_one_launch()
+                layer.check()
+            assert_close(layer.out.cpu(), ref, w.data_type, f"qwen3 with {S} tokens, one launch")
+        finally:
+            layer.close()
+
+
 def test_one_context_serves_several_layers():
     """Three layers of one model (same shapes, different weights) run through ONE context, in turn
     and repeatedly: every forward equals what a context of its own gives for that layer, bit for
