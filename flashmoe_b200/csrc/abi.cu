@@ -170,7 +170,7 @@ namespace {
 struct Plan {
   int round_ec = 0, landing_rows = 0, max_mtiles = 0;
   SymmLayout lay{};
-  size_t w_y = 0, w_split = 0, w_done = 0, w_split_done = 0, w_ctl = 0, w_status = 0, w_trace = 0, w_table = 0,
+  size_t w_y = 0, w_logits = 0, w_split = 0, w_done = 0, w_split_done = 0, w_ctl = 0, w_status = 0, w_trace = 0, w_table = 0,
          w_routes = 0, w_owner = 0, w_lidx = 0, w_local = 0, work_bytes = 0;
   int split_parts = 1, split_tiles = 0;
   size_t weight_plane_bytes = 0;   // fp32 layers: the BF16 planes of up, up_v and down
@@ -219,6 +219,7 @@ Plan plan_sizes(const fmoe_model_desc& m, int W, int nLx) {
   pl.split_parts = split_parts_for(m);
   pl.split_tiles = pl.split_parts > 1 ? kSplitTilesMax : 0;
   pl.w_split = w; w = align_up(w + static_cast<size_t>(pl.split_tiles) * pl.split_parts * kTileM * kUmmaN * sizeof(float), 1024);
+  pl.w_logits = w; w = align_up(w + sizeof(float) * S * E, 1024);
   pl.w_done = w; w = align_up(w + sizeof(uint32_t) * pl.max_mtiles, 256);
   pl.w_split_done = w; w = align_up(w + sizeof(uint32_t) * 4 * (pl.split_tiles + 1), 256);
   pl.w_ctl = w; w = align_up(w + 256, 256);   // ticket, done_ctas, abort, epoch
@@ -429,6 +430,7 @@ int fmoe_ctx_create(const fmoe_model_desc* model, const fmoe_ep_desc* ep, void* 
   p.gemm0_done = reinterpret_cast<uint32_t*>(c->work + w_done);
   p.split_scratch = reinterpret_cast<float*>(c->work + pl.w_split);
   p.split_done = reinterpret_cast<uint32_t*>(c->work + pl.w_split_done);
+  p.route_logits = reinterpret_cast<float*>(c->work + pl.w_logits);
   p.ticket = reinterpret_cast<uint32_t*>(c->work + w_ctl);
   p.done_ctas = reinterpret_cast<uint32_t*>(c->work + w_ctl + 64);
   p.abort_word = reinterpret_cast<uint32_t*>(c->work + w_ctl + 128);

@@ -94,6 +94,7 @@ struct MoeParams {
   const float* logit_bias;  // [E] or null
   float* routing;           // [S, E] probabilities out, or null
   int32_t* counts_out;      // [E] (the same array as expert_counts)
+  float* route_logits;      // [S, E] workspace of the routing phase
   unsigned long long* grid_bar;   // arrivals at the routing phase's grid barriers (zero between launches)
 
   // per forward

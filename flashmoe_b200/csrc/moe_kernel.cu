@@ -352,11 +352,11 @@ __device__ __forceinline__ void moe_forward_body(const MoeParams& p, const TmaMa
   // ---- routing inside the launch (optional) ----------------------------------------------
   // The router's two steps as phases of this kernel, for callers that want one launch per
   // layer (decode-sized batches, where two extra launches cost as much as the layer): every warp
-  // of the grid takes tokens and runs logits, softmax and top-k in the router kernels' own fp32
-  // order (lane l of the warp owns the 8-element vectors v = l mod 32 of H, ascending, one FMA per
-  // element; xor-butterfly fold), a grid barrier, every CTA takes experts and hands out slots in
-  // ascending token order, a second barrier.  The stage ring is idle until the first ticket and
-  // lends each warp a row of E floats.
+  // of the grid computes logits in the router kernels' own fp32 order (lane l of the warp owns the
+  // 8-element vectors v = l mod 32 of H, ascending, one FMA per element; xor-butterfly fold), a
+  // grid barrier, a warp per token runs softmax and top-k, a barrier, every CTA takes experts and
+  // hands out slots in ascending token order, a third barrier.  The stage ring is idle until the
+  // first ticket and lends each warp a row of E floats.
   if (p.router_w != nullptr) {
     auto grid_barrier = [&](unsigned long long target) {
       __syncthreads();
@@ -374,40 +374,51 @@ __device__ __forceinline__ void moe_forward_body(const MoeParams& p, const TmaMa
       __syncthreads();
     };
     {
+      // logits: one work item = one token against 8 experts, items dealt round-robin to the grid's
+      // warps (a single token still spreads over E / 8 warps)
       const T* __restrict__ X = static_cast<const T*>(p.tokens);
       const T* __restrict__ Wr = static_cast<const T*>(p.router_w);
-      float* row = reinterpret_cast<float*>(stages) + static_cast<size_t>(warp) * E;
       const int nvec = H_ >> 3, iters = (nvec + 31) >> 5;
-      Route* routes = const_cast<Route*>(p.routes);
-      for (int tok = blockIdx.x * (kThreads / 32) + warp; tok < p.S; tok += gridDim.x * (kThreads / 32)) {
-        for (int eg = 0; eg < E; eg += 8) {
-          float acc[8];
+      const int groups = E >> 3;
+      const int G = gridDim.x * (kThreads / 32);
+      for (int item = blockIdx.x * (kThreads / 32) + warp; item < p.S * groups; item += G) {
+        const int tok = item / groups, eg = (item - tok * groups) << 3;
+        float acc[8];
 #pragma unroll
-          for (int e = 0; e < 8; ++e) acc[e] = 0.0f;
-          for (int it = 0; it < iters; ++it) {
-            const int v = it * 32 + lane;
-            if (v < nvec) {
-              float xv[8];
-              Vec8<T>::load(X + static_cast<size_t>(tok) * H_ + v * 8, xv);
+        for (int e = 0; e < 8; ++e) acc[e] = 0.0f;
+#pragma unroll 2
+        for (int it = 0; it < iters; ++it) {
+          const int v = it * 32 + lane;
+          if (v < nvec) {
+            float xv[8];
+            Vec8<T>::load(X + static_cast<size_t>(tok) * H_ + v * 8, xv);
 #pragma unroll
-              for (int e = 0; e < 8; ++e) {
-                float wv[8];
-                Vec8<T>::load(Wr + static_cast<size_t>(eg + e) * H_ + v * 8, wv);
+            for (int e = 0; e < 8; ++e) {
+              float wv[8];
+              Vec8<T>::load(Wr + static_cast<size_t>(eg + e) * H_ + v * 8, wv);
 #pragma unroll
-                for (int j = 0; j < 8; ++j) {
-                  if constexpr (Vec8<T>::kExactProducts) acc[e] = __fmaf_rn(xv[j], wv[j], acc[e]);
-                  else acc[e] = __fadd_rn(acc[e], __fmul_rn(xv[j], wv[j]));
-                }
+              for (int j = 0; j < 8; ++j) {
+                if constexpr (Vec8<T>::kExactProducts) acc[e] = __fmaf_rn(xv[j], wv[j], acc[e]);
+                else acc[e] = __fadd_rn(acc[e], __fmul_rn(xv[j], wv[j]));
               }
             }
           }
-#pragma unroll
-          for (int e = 0; e < 8; ++e) {
-            const int ex = eg + e;
-            const float sum = butterfly_sum(acc[e]);
-            if (lane == (ex & 31)) row[ex] = p.logit_bias ? __fadd_rn(sum, __ldg(p.logit_bias + ex)) : sum;
-          }
         }
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          const float sum = butterfly_sum(acc[e]);
+          if (lane == e) __stcg(p.route_logits + static_cast<size_t>(tok) * E + eg + e,
+                                p.logit_bias ? __fadd_rn(sum, __ldg(p.logit_bias + eg + e)) : sum);
+        }
+      }
+    }
+    grid_barrier(gridDim.x);
+    if (ctl->ok) {
+      // softmax and top-k: one warp per token, the token's row of logits in shared memory
+      float* row = reinterpret_cast<float*>(stages) + static_cast<size_t>(warp) * E;
+      Route* routes = const_cast<Route*>(p.routes);
+      for (int tok = blockIdx.x * (kThreads / 32) + warp; tok < p.S; tok += gridDim.x * (kThreads / 32)) {
+        for (int j = lane; j < E; j += 32) row[j] = __ldcg(p.route_logits + static_cast<size_t>(tok) * E + j);
         __syncwarp();
         int idx;
         float weight;
@@ -416,7 +427,7 @@ __device__ __forceinline__ void moe_forward_body(const MoeParams& p, const TmaMa
         __syncwarp();
       }
     }
-    grid_barrier(gridDim.x);
+    grid_barrier(2ull * gridDim.x);
     if (ctl->ok) {
       // slots: one CTA per expert (strided), tokens in ascending order, kThreads at a time
       int* warp_tot = reinterpret_cast<int*>(stages);      // [warps] + running base
@@ -458,7 +469,7 @@ __device__ __forceinline__ void moe_forward_body(const MoeParams& p, const TmaMa
         if (tid == 0) p.counts_out[e] = warp_tot[8];
       }
     }
-    grid_barrier(2ull * gridDim.x);
+    grid_barrier(3ull * gridDim.x);
   }
 
   // ---- count exchange (CTA 0 publishes; everyone waits) --------------------------------

@@ -494,13 +494,9 @@ cudaError_t launch_topk_wide(const RouterParams& p, cudaStream_t stream) {
 
 template <typename T>
 cudaError_t launch_topk(const RouterParams& p, cudaStream_t stream) {
-  if (p.E >= 64 && p.E % 32 == 0) {
-    // with many experts: weights converted once per CTA, paired FMAs (router_topk_wide_kernel);
-    // TT = the most tokens per warp that still fills the SMs with warps
-    if (p.S >= 120 * 16) return launch_topk_wide<T, 4>(p, stream);
-    if (p.S >= 120 * 8) return launch_topk_wide<T, 2>(p, stream);
-    return launch_topk_wide<T, 1>(p, stream);
-  }
+  // many experts and enough tokens to fill the SMs four to a warp: weights converted once per CTA,
+  // paired FMAs (router_topk_wide_kernel); below that its per-CTA staging does not pay
+  if (p.E >= 64 && p.E % 32 == 0 && p.S >= 120 * 16) return launch_topk_wide<T, 4>(p, stream);
   if (p.E >= 64) {
     if (p.S >= 120 * 16) return launch_topk_eg<T, 4, 4, 4>(p, stream);
     if (p.S >= 120 * 8) return launch_topk_eg<T, 2, 4, 4>(p, stream);
