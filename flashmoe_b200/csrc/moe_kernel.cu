@@ -687,11 +687,12 @@ __device__ __forceinline__ void moe_forward_body(const MoeParams& p, const TmaMa
   // 1 are already drawing tickets and loading weights.  A GEMM0 ticket waits for the rows of its
   // own M tile only (per source, on disp_arrived) and the dispatch depends on no ticket, so the
   // order stays deadlock-free; the first epilogue is due one whole main loop after the first MMA.
-  auto send_rows = [&](const int v0, const RowInfo ri) {   // list entries v0 .. v0 + 31
+  // Sends the list entries [w0 + a, w0 + b) of the 32-entry window that starts at w0; `ri` holds
+  // the window's look-ups (lane i = entry w0 + i).
+  auto send_rows = [&](const int a, const int b, const RowInfo ri) {
     const int vecs = H_ * EB / 16;
     const uint4* tok_base = static_cast<const uint4*>(p.tokens);
-    const int n = min(32, n0 + n1 - v0);
-    for (int i = 0; i < n; ++i) {
+    for (int i = a; i < b; ++i) {
       const int pos = __shfl_sync(0xffffffffu, ri.pos, i);
       const int row = __shfl_sync(0xffffffffu, ri.row, i);
       const uint32_t token = __shfl_sync(0xffffffffu, ri.token, i);
@@ -740,11 +741,11 @@ __device__ __forceinline__ void moe_forward_body(const MoeParams& p, const TmaMa
     __syncwarp();
     if (lane == 0) { if (W > 1) fence_acq_rel_sys(); else fence_acq_rel_gpu(); }
     const int prev = __shfl_up_sync(0xffffffffu, ri.pos, 1);
-    unsigned heads = __ballot_sync(0xffffffffu, lane < n && (lane == 0 || prev != ri.pos));
+    unsigned heads = __ballot_sync(0xffffffffu, lane >= a && lane < b && (lane == a || prev != ri.pos));
     while (heads != 0) {
       const int h = __ffs(heads) - 1;
       heads &= heads - 1;
-      const int end = heads != 0 ? __ffs(heads) - 1 : n;      // the next run's first entry
+      const int end = heads != 0 ? __ffs(heads) - 1 : b;      // the next run's first entry
       const int pos = __shfl_sync(0xffffffffu, ri.pos, h);
       if (lane == 0) {
         const int e = tb.ord[pos];
@@ -975,15 +976,36 @@ __device__ __forceinline__ void moe_forward_body(const MoeParams& p, const TmaMa
       }
     }
   } else if (ctl->ok) {
-    for (int v0 = 0; v0 < n0 + n1; v0 += 32) send_rows(v0, v0 == 0 ? pre : lookup(v0));
-    if (warp == 2 && lane == 0) stamp_now(3);
-    // epilogue warps: TMEM lane quadrant = warp id mod 4; this CTA's 128 rows of the pair's tile
+    // epilogue warps: TMEM lane quadrant = warp id mod 4; this CTA's 128 rows of the pair's tile.
+    // They also carry the dispatch: rows are sent in batches of 16 for as long as no finished
+    // accumulator is waiting for them, so a long dispatch (many routed rows per warp) never keeps
+    // the MMA warp waiting for a free TMEM buffer.
     const int quad = warp & 3;
     const int row_in_tile = quad * 32 + lane;
     uint32_t acc_empty_leader = 0;
     if constexpr (kPair) acc_empty_leader = map_to_cta(&ctl->acc_empty[0], 0);
     uint32_t tslot = 0, acc_it = 0;
+    const int nsend = n0 + n1;
+    int sent = 0;
+    RowInfo win = pre;               // look-ups of the window [sent & ~31, +32)
+    if (nsend == 0 && warp == 2 && lane == 0) stamp_now(3);
     for (uint32_t it = 0;; ++it, tslot = (tslot + 1) % kTaskSlots) {
+      while (sent < nsend) {
+        // lane 0 looks: is the next task known, and (unless it is the stop task) its accumulator full?
+        int ready = 0;
+        if (lane == 0 && mbar_try_wait(&ctl->task_full[tslot], (it / kTaskSlots) & 1)) {
+          const uint32_t b = acc_it % kBufs;
+          ready = ctl->tasks[tslot].kind != kTaskStop &&
+                  mbar_try_wait_cluster(&ctl->acc_full[b], (acc_it / kBufs) & 1);
+        }
+        if (__shfl_sync(0xffffffffu, ready, 0)) break;
+        const int w0 = sent & ~31;
+        const int upto = min(min(sent + 16, w0 + 32), nsend);
+        send_rows(sent - w0, upto - w0, win);
+        sent = upto;
+        if (sent < nsend && (sent & 31) == 0) win = lookup(sent);
+        if (sent == nsend && warp == 2 && lane == 0) stamp_now(3);
+      }
       if (!mbar_wait(&ctl->task_full[tslot], (it / kTaskSlots) & 1, wc)) {
         fail(p, FMOE_PHASE_TASK, -2); break;
       }
