@@ -267,13 +267,19 @@ def spot_parity(w, layer, lw, mine, x, dev, n_spot):
 
 
 def roofline_of(w, world, mine, allc, ms_kernel, peaks, peaks_kind):
-    """The fused kernel against the slower of its tensor and HBM bounds on this rank."""
+    """The fused kernel against the slower of its tensor and HBM bounds.  The launch time is the
+    maximum over ranks, so the work is that of the rank with the most routed pairs (with balanced
+    routing every rank has about the same; with a skewed router one rank carries the layer)."""
     from flashmoe_b200.jit import DataType, MLPType
     from flashmoe_b200.workloads import weight_bytes_per_rank
     S, H, I = w.tokens_per_rank, w.token_dim, w.ffn_size
     eb = 4 if w.data_type == DataType.FP32 else 2
     cap = w.expert_peer_capacity
-    pairs_here = sum(min(c[e], cap) for c in allc for e in mine)
+    nlx = len(mine)
+    per_rank = [sum(min(c[e], cap) for c in allc for e in range(r * nlx, (r + 1) * nlx)) for r in range(world)]
+    busiest = max(range(world), key=lambda r: per_rank[r])
+    mine = list(range(busiest * nlx, (busiest + 1) * nlx))
+    pairs_here = per_rank[busiest]
     active = sum(1 for e in mine if any(c[e] > 0 for c in allc))   # experts whose weights are read
     c_mlp = 6 if w.mlp_type == MLPType.GATED else 4
     flops = float(pairs_here) * c_mlp * H * I
@@ -291,7 +297,7 @@ def roofline_of(w, world, mine, allc, ms_kernel, peaks, peaks_kind):
             "frac": ach / peak, "peak_source": f"of {peaks_kind}",
             "traffic": load_traffic(w.name, world), "ms_per_launch": ms_kernel,
             "algorithmic_flops": flops, "algorithmic_hbm_bytes": hbm_bytes,
-            "active_local_experts": active, "routed_pairs": pairs_here,
+            "active_local_experts": active, "routed_pairs": pairs_here, "routed_pairs_per_rank": per_rank,
             "t_tensor_us": t_tensor * 1e6, "t_hbm_us": t_hbm * 1e6,
             "pct_dense_bf16_peak_burst": 100.0 * tensor_flops / sec / (peaks["bf16_tflops"] * 1e12)}
 

@@ -38,7 +38,7 @@ class _MoEModule:
         self._lib, self._desc, self._topo = lib, desc, topo
 
     def initialize(self, num_experts, expert_peer_capacity, ep_world, my_pe, ep_rank, local_rank,
-                   num_local_experts, expert_map, rank_map, stream_ptr) -> int:
+                   num_local_experts, expert_map, rank_map, stream_ptr, memory=None) -> int:
         if len(expert_map) != num_experts:
             raise ValueError("expert_map.size() != num_experts")
         if len(rank_map) != ep_world:
@@ -47,8 +47,13 @@ class _MoEModule:
         rmap = (C.c_int32 * ep_world)(*rank_map)
         ep = N.EpDesc(ep_world, ep_rank, my_pe, local_rank, num_local_experts, int(self._topo), emap, rmap)
         ctx = C.c_void_p()
-        N.check(self._lib.fmoe_ctx_create(C.byref(self._desc), C.byref(ep), C.c_void_p(stream_ptr),
-                                          C.byref(ctx)), "initialize")
+        if memory is None:
+            N.check(self._lib.fmoe_ctx_create(C.byref(self._desc), C.byref(ep), C.c_void_p(stream_ptr),
+                                              C.byref(ctx)), "initialize")
+        else:   # (symmetric address, bytes, workspace address, bytes): the caller's device memory
+            N.check(self._lib.fmoe_ctx_create_in(C.byref(self._desc), C.byref(ep), C.c_void_p(stream_ptr),
+                                                 C.c_void_p(memory[0]), memory[1], C.c_void_p(memory[2]), memory[3],
+                                                 C.byref(ctx)), "initialize")
         if ep_world > 1:
             handle = (C.c_ubyte * N.IPC_HANDLE_BYTES)()
             N.check(self._lib.fmoe_symm_export(ctx, handle), "initialize (export)")
@@ -119,8 +124,11 @@ class _MoEModule:
                    C.byref(ra), C.byref(fa), C.c_void_p(fargs.stream_ptr)), "forward_host")
 
 
-def initialize(arg: InitArgs) -> ContextHandle:
+def initialize(arg: InitArgs, memory=None) -> ContextHandle:
     """Create this rank's context (flashmoe/__init__.py:7-77).
+
+    `memory` = (symmetric address, bytes, workspace address, bytes) places the context in device
+    memory the caller owns (sizes from `get_workspace_bytes`); by default the library allocates.
 
     With `ep_rank` unset the group is taken from the communication bootstrap and experts are
     blocked over the ranks (`expert_map[i] = i // num_local_experts`); the fields are written
@@ -144,7 +152,8 @@ def initialize(arg: InitArgs) -> ContextHandle:
     ctx = mod.initialize(num_experts=arg.num_experts, expert_peer_capacity=arg.expert_peer_capacity,
                          ep_world=arg.ep_world, my_pe=arg.my_pe, ep_rank=arg.ep_rank,
                          local_rank=arg.device_id, num_local_experts=arg.num_local_experts,
-                         expert_map=arg.expert_map, rank_map=arg.rank_map, stream_ptr=arg.stream_ptr)
+                         expert_map=arg.expert_map, rank_map=arg.rank_map, stream_ptr=arg.stream_ptr,
+                         memory=memory)
     # the kernel specialised for this description, when the cache holds it (or FMOE_JIT=1 builds it);
     # FMOE_JIT=off keeps the generic kernel
     if os.environ.get("FMOE_JIT", "0") != "off":

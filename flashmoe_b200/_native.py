@@ -64,6 +64,8 @@ class Geometry(C.Structure):
 SIGNATURES = {
     "fmoe_ctx_create": (C.c_int, [C.POINTER(ModelDesc), C.POINTER(EpDesc), C.c_void_p,
                                   C.POINTER(C.c_void_p)]),
+    "fmoe_ctx_create_in": (C.c_int, [C.POINTER(ModelDesc), C.POINTER(EpDesc), C.c_void_p, C.c_void_p, C.c_size_t,
+                                     C.c_void_p, C.c_size_t, C.POINTER(C.c_void_p)]),
     "fmoe_workspace_bytes": (C.c_int, [C.POINTER(ModelDesc), C.POINTER(EpDesc), C.POINTER(C.c_int64),
                                        C.POINTER(C.c_int64)]),
     "fmoe_symm_bytes": (C.c_int, [C.c_void_p, C.POINTER(C.c_size_t)]),

@@ -88,6 +88,7 @@ struct fmoe_ctx {
   char* peers[FMOE_MAX_WORLD] = {};     // mapped blocks (peers[rank] == symm)
   bool imported[FMOE_MAX_WORLD] = {};   // opened through IPC (must be closed)
   bool committed = false;
+  bool owns_memory = true;              // false: symmetric block and workspace belong to the caller
   bool poisoned = false;                // a forward of this context ran out of a device-side wait
   char* work = nullptr;                 // private workspace, one allocation
   size_t work_bytes = 0;
@@ -230,7 +231,7 @@ Plan plan_sizes(const fmoe_model_desc& m, int W, int nLx) {
   pl.w_owner = w; w = align_up(w + sizeof(int32_t) * E, 256);
   pl.w_lidx = w; w = align_up(w + sizeof(int32_t) * E, 256);
   pl.w_local = w; w = align_up(w + sizeof(int32_t) * W * nLx, 256);
-  pl.work_bytes = w;
+  pl.work_bytes = align_up(w, 1024);   // what follows it (the BF16 weight planes of fp32 layers) stays aligned
   if (planes == 3)
     pl.weight_plane_bytes = static_cast<size_t>(nLx) * I * H * 2 * 3 * (m.mlp_type == FMOE_MLP_GATED ? 3 : 2);
   return pl;
@@ -260,9 +261,11 @@ void free_ctx(fmoe_ctx* c) {
   if (c == nullptr) return;
   for (int r = 0; r < FMOE_MAX_WORLD; ++r)
     if (c->imported[r] && c->peers[r] != nullptr) cudaIpcCloseMemHandle(c->peers[r]);
-  if (c->symm) cudaFree(c->symm);
-  if (c->work) cudaFree(c->work);
-  if (c->wsplit) cudaFree(c->wsplit);
+  if (c->owns_memory) {
+    if (c->symm) cudaFree(c->symm);
+    if (c->work) cudaFree(c->work);
+    if (c->wsplit) cudaFree(c->wsplit);
+  }
   if (c->stage_tokens) cudaFree(c->stage_tokens);
   if (c->stage_out) cudaFree(c->stage_out);
   if (c->spec_handle) dlclose(c->spec_handle);
@@ -304,11 +307,28 @@ int fmoe_workspace_bytes(const fmoe_model_desc* model, const fmoe_ep_desc* ep, i
   if (rc != FMOE_OK) return rc;
   const Plan pl = plan_sizes(*model, ep->ep_world, ep->num_local_experts);
   if (symm_bytes_out) *symm_bytes_out = static_cast<int64_t>(pl.lay.total);
-  if (workspace_bytes_out) *workspace_bytes_out = static_cast<int64_t>(pl.work_bytes + pl.weight_plane_bytes);
+  if (workspace_bytes_out) *workspace_bytes_out = static_cast<int64_t>(align_up(pl.work_bytes, 1024) + pl.weight_plane_bytes);
   return FMOE_OK;
 }
 
+static int ctx_create_impl(const fmoe_model_desc* model, const fmoe_ep_desc* ep, void* stream, void* symm_mem,
+                           size_t symm_bytes, void* work_mem, size_t work_bytes, bool caller_memory, fmoe_ctx** out);
+
 int fmoe_ctx_create(const fmoe_model_desc* model, const fmoe_ep_desc* ep, void* stream, fmoe_ctx** out) {
+  return ctx_create_impl(model, ep, stream, nullptr, 0, nullptr, 0, false, out);
+}
+
+int fmoe_ctx_create_in(const fmoe_model_desc* model, const fmoe_ep_desc* ep, void* stream, void* symm_mem,
+                       size_t symm_bytes, void* work_mem, size_t work_bytes, fmoe_ctx** out) {
+  if (symm_mem == nullptr || work_mem == nullptr)
+    return set_error(FMOE_ERR_INVALID_ARG, "symmetric block and workspace are required");
+  if ((reinterpret_cast<uintptr_t>(symm_mem) | reinterpret_cast<uintptr_t>(work_mem)) & 1023)
+    return set_error(FMOE_ERR_INVALID_ARG, "symmetric block and workspace must be 1024-byte aligned");
+  return ctx_create_impl(model, ep, stream, symm_mem, symm_bytes, work_mem, work_bytes, true, out);
+}
+
+static int ctx_create_impl(const fmoe_model_desc* model, const fmoe_ep_desc* ep, void* stream, void* symm_mem,
+                           size_t symm_bytes, void* work_mem, size_t work_bytes, bool caller_memory, fmoe_ctx** out) {
   if (out == nullptr) return set_error(FMOE_ERR_INVALID_ARG, "out is null");
   *out = nullptr;
   int rc = check_layer(model, ep);
@@ -364,7 +384,20 @@ int fmoe_ctx_create(const fmoe_model_desc* model, const fmoe_ep_desc* ep, void* 
   L = pl.lay;
   g.symm_bytes = static_cast<int64_t>(L.total);
 
-  ce = cudaMalloc(&c->symm, L.total);
+  c->owns_memory = !caller_memory;
+  if (caller_memory) {
+    const size_t need_work = align_up(pl.work_bytes, 1024) + pl.weight_plane_bytes;
+    if (symm_bytes < L.total || work_bytes < need_work) {
+      free_ctx(c);
+      return set_error(FMOE_ERR_INVALID_ARG, "caller's memory is too small: this layer needs " + std::to_string(L.total) +
+                                                 " bytes of symmetric block and " + std::to_string(need_work) +
+                                                 " bytes of workspace (see fmoe_workspace_bytes)");
+    }
+    c->symm = static_cast<char*>(symm_mem);
+    ce = cudaSuccess;
+  } else {
+    ce = cudaMalloc(&c->symm, L.total);
+  }
   if (ce != cudaSuccess) { free_ctx(c); return set_error(FMOE_ERR_NO_MEMORY, std::string("symmetric block: ") + cudaGetErrorString(ce)); }
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   // control words must start at zero; the data areas need no initial value
@@ -379,7 +412,8 @@ int fmoe_ctx_create(const fmoe_model_desc* model, const fmoe_ep_desc* ep, void* 
                w_local = pl.w_local, w = pl.work_bytes;
   c->work_bytes = w;
   g.workspace_bytes = static_cast<int64_t>(w);
-  ce = cudaMalloc(&c->work, w);
+  if (caller_memory) c->work = static_cast<char*>(work_mem);
+  else ce = cudaMalloc(&c->work, w);
   if (ce != cudaSuccess) { free_ctx(c); return set_error(FMOE_ERR_NO_MEMORY, std::string("workspace: ") + cudaGetErrorString(ce)); }
   ce = cudaMemsetAsync(c->work + w_done, 0, w - w_done, st);
   if (ce == cudaSuccess) ce = cudaMemcpyAsync(c->work + w_owner, c->owner.data(), sizeof(int32_t) * E, cudaMemcpyHostToDevice, st);
@@ -449,7 +483,8 @@ int fmoe_ctx_create(const fmoe_model_desc* model, const fmoe_ep_desc* ep, void* 
     // context owns, so their tensor maps are built once here
     const size_t mat = static_cast<size_t>(nLx) * I * H * 2 * 3;
     c->wsplit_up = 0; c->wsplit_up_v = gated ? mat : 0; c->wsplit_down = gated ? 2 * mat : mat;
-    ce = cudaMalloc(&c->wsplit, c->wsplit_down + mat);
+    if (caller_memory) c->wsplit = c->work + align_up(pl.work_bytes, 1024);   // behind the workspace proper
+    else ce = cudaMalloc(&c->wsplit, c->wsplit_down + mat);
     if (ce != cudaSuccess) { free_ctx(c); return set_error(FMOE_ERR_NO_MEMORY, std::string("weight planes: ") + cudaGetErrorString(ce)); }
     g.workspace_bytes += static_cast<int64_t>(c->wsplit_down + mat);
     rc = make_map(&c->maps[2], 1, c->wsplit + c->wsplit_up, 3ull * nLx * I, H);

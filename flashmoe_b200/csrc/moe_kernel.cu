@@ -75,6 +75,8 @@ struct Task {
   int part, nparts, split_idx;
 };
 
+constexpr uint32_t kRetStageBytes = 4 * 2048;
+
 struct Control {
   uint64_t full[6], empty[6];   // ring depth: 6 in pair mode, 4 alone
   uint64_t acc_full[kAccBufs], acc_empty[kAccBufs];
@@ -194,18 +196,6 @@ __device__ __forceinline__ void store_operand32(char* row, int col0, const float
     }
   }
 }
-// 32 consecutive columns of one row of an Element buffer (the return rows).
-template <typename T>
-__device__ __forceinline__ void store_result32(char* row, int col0, const float (&v)[32]) {
-  if constexpr (Elem<T>::kBytes == 2) {
-    store_operand32<T>(row, col0, v, 0);
-  } else {
-    float4* dst = reinterpret_cast<float4*>(row + static_cast<size_t>(col0) * 4);
-#pragma unroll
-    for (int q = 0; q < 8; ++q) dst[q] = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
-  }
-}
-
 template <bool kPrecise>
 __device__ __forceinline__ float activate_t(float x, int act) {
   switch (act) {
@@ -275,7 +265,9 @@ __device__ __forceinline__ void moe_forward_body(const MoeParams& p, const TmaMa
   // stage ring first, 1024-byte aligned (128-byte swizzle atoms)
   uint8_t* stages = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                                ~static_cast<uintptr_t>(1023));
-  Control* ctl = reinterpret_cast<Control*>(stages + NS * STAGE);
+  // 2 KB per epilogue warp: expert output rows pass through here so that they leave as whole lines
+  uint4* ret_stage = reinterpret_cast<uint4*>(stages + NS * STAGE);
+  Control* ctl = reinterpret_cast<Control*>(stages + NS * STAGE + kRetStageBytes);
   int* tab = reinterpret_cast<int*>(ctl + 1);
   Tables tb;
   {
@@ -1153,13 +1145,66 @@ __device__ __forceinline__ void moe_forward_body(const MoeParams& p, const TmaMa
           const float4* parts = reinterpret_cast<const float4*>(
                                     p.split_scratch + static_cast<size_t>(t.split_idx) * p.split_parts * kTileFloats) +
                                 row_in_tile;
-          auto finish_chunk = [&](int c, float (&o)[32]) {   // bias, rounding, the row's 32 columns
+          // Bias, rounding, and the row's 32 columns on their way to the token's owner.  A lane holds
+          // 32 columns of ITS row, so a warp-wide store straight from registers would be 32 pieces of
+          // 16 bytes in 32 different rows, which is the worst shape for a write that may cross
+          // NVLink.  The chunk is transposed through 2 KB of shared memory instead (16-byte pieces,
+          // xor-swizzled against bank conflicts) and leaves as 64-byte (16-bit types: 8 rows per
+          // instruction) or 128-byte (fp32: 4 rows per instruction) runs of one row each.
+          uint4* stage_w = ret_stage + (warp - 2) * 128;
+          const uint32_t orow_lo = static_cast<uint32_t>(reinterpret_cast<uintptr_t>(orow));
+          const uint32_t orow_hi = static_cast<uint32_t>(reinterpret_cast<uintptr_t>(orow) >> 32);
+          auto row_ptr = [&](int r) -> char* {      // row r's destination, from the lane that owns it
+            const uint32_t lo = __shfl_sync(0xffffffffu, orow_lo, r), hi = __shfl_sync(0xffffffffu, orow_hi, r);
+            return reinterpret_cast<char*>((static_cast<uintptr_t>(hi) << 32) | lo);
+          };
+          auto finish_chunk = [&](int c, float (&o)[32]) {   // every lane of the warp calls this
             const int col0 = col_base + c * 32;
-            if (valid && col0 < H_) {
+            if (col0 >= H_) return;
+            if (valid) {
 #pragma unroll
               for (int i = 0; i < 32; ++i)
                 o[i] += bias_at<T>(p.bias_down, static_cast<size_t>(t.lx) * H_ + col0 + i);
-              store_result32<T>(orow, col0, o);
+            }
+            if constexpr (EB == 2) {
+              uint4* mine = stage_w + lane * 4;
+              const int sw = (lane >> 1) & 3;
+#pragma unroll
+              for (int q = 0; q < 4; ++q)
+                mine[q ^ sw] = make_uint4(Cvt<T>::pack(o[8 * q], o[8 * q + 1]), Cvt<T>::pack(o[8 * q + 2], o[8 * q + 3]),
+                                          Cvt<T>::pack(o[8 * q + 4], o[8 * q + 5]), Cvt<T>::pack(o[8 * q + 6], o[8 * q + 7]));
+              __syncwarp();
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                const int r = 8 * i + (lane >> 2), piece = lane & 3;
+                const uint4 v = stage_w[r * 4 + (piece ^ ((r >> 1) & 3))];
+                char* dst = row_ptr(r);
+                const bool ok = __shfl_sync(0xffffffffu, valid ? 1 : 0, r) != 0;
+                if (ok) *reinterpret_cast<uint4*>(dst + static_cast<size_t>(col0) * 2 + piece * 16) = v;
+              }
+              __syncwarp();
+            } else {
+#pragma unroll
+              for (int pass = 0; pass < 2; ++pass) {
+                if ((lane >> 4) == pass) {
+                  const int r16 = lane & 15;
+                  uint4* mine = stage_w + r16 * 8;
+#pragma unroll
+                  for (int q = 0; q < 8; ++q)
+                    mine[q ^ (r16 & 7)] = make_uint4(__float_as_uint(o[4 * q]), __float_as_uint(o[4 * q + 1]),
+                                                     __float_as_uint(o[4 * q + 2]), __float_as_uint(o[4 * q + 3]));
+                }
+                __syncwarp();
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                  const int r16 = 4 * i + (lane >> 3), piece = lane & 7, r = pass * 16 + r16;
+                  const uint4 v = stage_w[r16 * 8 + (piece ^ (r16 & 7))];
+                  char* dst = row_ptr(r);
+                  const bool ok = __shfl_sync(0xffffffffu, valid ? 1 : 0, r) != 0;
+                  if (ok) *reinterpret_cast<uint4*>(dst + static_cast<size_t>(col0) * 4 + piece * 16) = v;
+                }
+                __syncwarp();
+              }
             }
           };
           if (!split) {
@@ -1182,8 +1227,9 @@ __device__ __forceinline__ void moe_forward_body(const MoeParams& p, const TmaMa
               for (int i = 0; i < 32; ++i) o[i] = __uint_as_float(a[i]);
               finish_chunk(c, o);
             }
-          } else if (valid) {
+          } else {
             // two chunks per step: the parked sums of both are in flight before either is added up
+            // (rows past the tile's end read parked garbage that is never stored)
 #pragma unroll 1
             for (int c = 0; c < kUmmaN / 32; c += 2) {
               float o[2][32];
@@ -1389,7 +1435,7 @@ moe_forward_kernel(const __grid_constant__ MoeParams p, const __grid_constant__ 
 }  // namespace
 
 size_t moe_smem_bytes(int W, int E, int nLx) {
-  return 1024 + static_cast<size_t>(4) * 3 * kStageABytes + sizeof(Control) +
+  return 1024 + static_cast<size_t>(4) * 3 * kStageABytes + kRetStageBytes + sizeof(Control) +
          tables_ints(W, E, nLx) * sizeof(int) + 64;
 }
 

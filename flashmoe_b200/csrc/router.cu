@@ -496,6 +496,7 @@ template <typename T>
 cudaError_t launch_topk(const RouterParams& p, cudaStream_t stream) {
   // many experts and enough tokens to fill the SMs four to a warp: weights converted once per CTA,
   // paired FMAs (router_topk_wide_kernel); below that its per-CTA staging does not pay
+  // (two tokens per warp and two CTAs per SM measured slower: 303 vs 262 us at Qwen3 shapes, 8192 tokens)
   if (p.E >= 64 && p.E % 32 == 0 && p.S >= 120 * 16) return launch_topk_wide<T, 4>(p, stream);
   if (p.E >= 64) {
     if (p.S >= 120 * 16) return launch_topk_eg<T, 4, 4, 4>(p, stream);

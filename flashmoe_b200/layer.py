@@ -17,7 +17,7 @@ from .workloads import TORCH_DTYPE, LayerWeights, Workload
 class MoELayer:
     def __init__(self, w: Workload, weights: LayerWeights, device_id: int = 0, *,
                  stream: Optional[torch.cuda.Stream] = None, return_logits: bool = False,
-                 local_experts: Optional[range] = None):
+                 local_experts: Optional[range] = None, memory=None):
         """`weights` holds either all E experts (this rank's slice is taken from it) or, when
         `local_experts` is given, exactly that slice."""
         self.w = w
@@ -30,7 +30,7 @@ class MoELayer:
             ffn_size=w.ffn_size, num_experts=w.num_experts, top_k=w.top_k, gpu_arch=1000,
             mlp_type=w.mlp_type, act_type=w.act_type, stream_ptr=sp, device_id=device_id,
             expert_peer_capacity=w.expert_peer_capacity)
-        self.handle = flashmoe.initialize(self.args)
+        self.handle = flashmoe.initialize(self.args, memory=memory)
         self.router_handle = flashmoe.router.initialize(self.args, return_logits=return_logits)
         a = self.args
         if local_experts is None:

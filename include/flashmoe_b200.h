@@ -125,6 +125,17 @@ int fmoe_ctx_create(const fmoe_model_desc* model, const fmoe_ep_desc* ep, void* 
 int fmoe_workspace_bytes(const fmoe_model_desc* model, const fmoe_ep_desc* ep,
                          int64_t* symm_bytes_out, int64_t* workspace_bytes_out);
 
+/* The same with memory the CALLER owns, sized by fmoe_workspace_bytes (the reference's
+ * getWorkspaceBytes exists so that a serving engine can budget, bootstrap.cuh:377-410; here it can
+ * also place): `symm_mem` (>= symm bytes) becomes the symmetric block, `work_mem` (>= workspace
+ * bytes) the private workspace; both 1024-byte aligned device memory, and `symm_mem` the start of
+ * an allocation of its own when other ranks are to map it (CUDA IPC shares whole allocations).
+ * Nothing is allocated on the device by this call or by fmoe_forward / fmoe_router_forward on the
+ * context, and fmoe_ctx_destroy leaves the two blocks to the caller.  (The host-buffer entry
+ * points fmoe_forward_host* still allocate their staging buffers on first use.) */
+int fmoe_ctx_create_in(const fmoe_model_desc* model, const fmoe_ep_desc* ep, void* stream, void* symm_mem,
+                       size_t symm_bytes, void* work_mem, size_t work_bytes, fmoe_ctx** out);
+
 /* Replaces nvshmem_malloc + nvshmem_ptr (bootstrap.cuh:141-151, 239-249): the symmetric
  * block is an ordinary device allocation shared through CUDA IPC.  Export this rank's
  * handle, gather the handles by any host-side means, import every peer's, then commit.

@@ -167,6 +167,53 @@ def test_router_inside_the_launch_at_decode_sizes():
             layer.close()
 
 
+@pytest.mark.parametrize("name", ["bf16_gated_k2", "fp32_gated_k2"])
+def test_context_in_memory_the_caller_owns(name):
+    """fmoe_ctx_create_in: the symmetric block and the workspace are the caller's (sized by the
+    host-side query); creating the context and running forwards takes no device memory, the
+    results are those of a context that allocated for itself, and destroying it leaves the
+    caller's blocks alone."""
+    import flashmoe_b200 as flashmoe
+    from flashmoe_b200.layer import MoELayer
+    w = GOLDEN_CASES[name]
+    lw, x = make_weights(w), make_tokens(w)
+    own = make_layer(w, lw)
+    try:
+        want = own.forward(x).cpu()
+        need = flashmoe.get_workspace_bytes(own.args)
+    finally:
+        own.close()
+    symm = torch.empty(need["symmetric"] + 1024, dtype=torch.uint8, device="cuda")
+    work = torch.empty(need["workspace"] + 1024, dtype=torch.uint8, device="cuda")
+    up = lambda t: (t.data_ptr() + 1023) // 1024 * 1024
+    memory = (up(symm), need["symmetric"], up(work), need["workspace"])
+    # creating (and destroying) a context inside the caller's blocks takes no device memory
+    import ctypes as C
+    from flashmoe_b200 import _native as N
+    a = own.args
+    ep = N.EpDesc(1, 0, 0, 0, w.num_experts, 0, (C.c_int32 * w.num_experts)(*([0] * w.num_experts)), (C.c_int32 * 1)(0))
+    desc, raw = flashmoe._model_desc(a), C.c_void_p()
+    torch.cuda.synchronize()
+    free0, _ = torch.cuda.mem_get_info()
+    assert N.lib().fmoe_ctx_create_in(C.byref(desc), C.byref(ep), None, C.c_void_p(memory[0]), memory[1],
+                                      C.c_void_p(memory[2]), memory[3], C.byref(raw)) == 0, N.lib().fmoe_last_error()
+    torch.cuda.synchronize()
+    assert torch.cuda.mem_get_info()[0] == free0
+    assert N.lib().fmoe_ctx_destroy(raw, None) == 0
+    layer = MoELayer(w, lw, memory=memory)
+    try:
+        got = layer.forward(x).cpu()
+        assert torch.equal(got, want)
+        assert torch.equal(layer.forward(x).cpu(), want)
+    finally:
+        layer.close()
+    # too little memory is refused with the sizes in the message
+    with pytest.raises(flashmoe.FlashMoEError) as err:
+        MoELayer(w, lw, memory=(memory[0], 4096, memory[2], memory[3]))
+    assert str(need["symmetric"]) in str(err.value)
+    del symm, work
+
+
 def test_one_context_serves_several_layers():
     """Three layers of one model (same shapes, different weights) run through ONE context, in turn
     and repeatedly: every forward equals what a context of its own gives for that layer, bit for
