@@ -49,6 +49,11 @@ def main():
             frac, _ = elementwise_mismatch(out, ref, w.data_type)
             worst, worst_frac = max(worst, err), max(worst_frac, frac)
             ok = ok and bool(torch.isfinite(out.float()).all()) and err <= REL_TOL[int(w.data_type)] and frac == 0.0
+        # the same step as ONE launch per rank (the router as the kernel's first phase): same bits
+        layer.out.zero_()
+        layer.step_one_launch()
+        layer.check()
+        ok = ok and bool(torch.equal(layer.out.cpu(), out))
     finally:
         layer.close()
     res = [None] * world
