@@ -18,9 +18,12 @@
 //    global counter over a fixed task order (GEMM0 of expert i, then GEMM1 of expert i-lag)
 //    and waits on the task's readiness counters itself.  Tickets are handed out in an order
 //    in which a task only ever waits on tasks with smaller tickets, so the kernel cannot
-//    deadlock as long as all CTAs are co-resident (grid <= SM count, one CTA per SM).
+//    deadlock as long as all CTAs are co-resident (grid <= SM count, one CTA per SM), which the
+//    cooperative launch guarantees.
 //  * Each CTA is warp-specialised: warp 0 = scheduler + TMA producer, warp 1 = UMMA issuer and
-//    TMEM owner, warps 2..5 = epilogue.  By default every CTA works alone on 128 x 256 output
+//    TMEM owner, warps 2..5 = dispatch and epilogue: they push this rank's routed rows to the
+//    experts' owners in batches, between epilogues, while warps 0 and 1 already work on the
+//    first tiles whose rows are in.  By default every CTA works alone on 128 x 256 output
 //    tiles (tcgen05.mma.cta_group::1, M = 128, N = 256): a 4-stage TMA->UMMA ring of 48 KB stages
 //    (A tile 128 x 64, B tile 256 x 64) and a double-buffered 2 x 256-column TMEM accumulator
 //    overlap loads, MMA and epilogue.  A second form of the same body (opt-in) runs CTA pairs,
@@ -34,9 +37,16 @@
 //    (processor.cuh:97-136).  Rounding points are the reference's: the activated gate value
 //    is rounded to Element, the product is rounded to Element, the GEMM1 output is rounded
 //    to Element.
-//  * Expert outputs return to the token's owner as rows indexed by (token, choice); the owner
-//    sums a token's k rows in fp32 in selection order and rounds once (the reference
-//    accumulates with Element-precision atomics in arrival order, combine.cuh:120-223).
+//  * Expert outputs return to the token's owner as rows indexed by (token, choice), written as
+//    whole 64/128-byte runs of one row through a shared-memory transpose; the owner sums a
+//    token's k rows in fp32 in selection order and rounds once (the reference accumulates with
+//    Element-precision atomics in arrival order, combine.cuh:120-223).
+//  * The last GEMM1 tiles of the task order are cut along K into parts whose fp32 partial sums
+//    are added in part order by whichever part finishes last, so the kernel ends on short
+//    tickets without losing run-to-run reproducibility.
+//  * Every signal that crosses CTAs or GPUs is one fence followed by relaxed counter updates
+//    (per batch of dispatched rows, per GEMM1 epilogue), not a release per update.
+//  * Optionally the launch opens with the router itself (three grid-wide phases).
 //
 // Every wait is bounded; a wait that runs out records where in `status`, raises the
 // kernel-wide abort word and every role leaves through the common exit (TMEM freed).
