@@ -806,6 +806,19 @@ def main() -> int:
     del layer, lw
     torch.cuda.empty_cache()
 
+    # --- the unfused NCCL pipeline on the same GPUs, briefly (5 timed steps), for the ratio ----------
+    vs_unfused = None
+    if not a.proxy_ep:
+        try:
+            u = unfused_arm(argparse.Namespace(steps=5, warmup=3), w, world, rank, local_rank, dev, dist, cfg)
+            if u is not None:
+                vs_unfused = {"unfused_ms_per_step": u["ms_per_step"], "fused_ms_per_step": ms_step,
+                              "ratio": u["ms_per_step"] / ms_step, "max_rel_diff_vs_fused": u["max_rel_diff_vs_fused"],
+                              "what": "bench.py --impl nccl_unfused, 5 timed steps in this run"}
+        except Exception as exc:
+            vs_unfused = {"error": f"{type(exc).__name__}: {exc}"[:200]}
+        torch.cuda.empty_cache()
+
     # --- the other benchmark shapes, briefly, at the same N -----------------------------------------
     others = None
     if a.others:
@@ -845,7 +858,8 @@ def main() -> int:
                     "api": "fmoe_forward_host_async + fmoe_forward_host_wait (C ABI, pinned host buffers; "
                            "copies of neighbouring steps overlap the kernels)"},
             "gpu_launches": int(launches), "parity": parity, "phases_us": phases, "nvlink": nvlink,
-            "roofline": roofline, "cpu_baseline": cpu, "clocks": clocks, "other_workloads": others}
+            "roofline": roofline, "cpu_baseline": cpu, "clocks": clocks, "vs_unfused": vs_unfused,
+            "other_workloads": others}
     if a.proxy_ep:
         line["proxy"] = f"one GPU carrying the expert load of one rank at EP={a.proxy_ep}; not a reported number"
     print(json.dumps(line))
