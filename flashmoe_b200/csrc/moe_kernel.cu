@@ -631,29 +631,25 @@ __device__ __forceinline__ void moe_forward_body(const MoeParams& p, const TmaMa
     }
   }
   __syncthreads();
+  // From here on the warps part: what is left of the tables (M-tile prefix, task order) is read by
+  // the scheduler only, so warp 0 builds it alone while the epilogue warps already send rows.
   if (ctl->ok && warp == 0) {
     const int mt = warp_scan([&](int lx) { return (tb.lx_rows[lx] + kTileM - 1) / kTileM; },
                              [&](int lx, int v) { tb.lx_mt0[lx] = v; }, nLx);
-    if (lane == 0) {
-      tb.lx_mt0[nLx] = mt;
-      ctl->lag = nLx;
-    }
-  }
-  __syncthreads();
-  // task order: GEMM1 of expert i trails GEMM0 of expert i by `lag` experts, the smallest lag
-  // whose GEMM0 tiles cover two tickets per CTA, so that by the time a GEMM1 ticket is drawn the
-  // GEMM0 tiles it depends on are long finished: G0(0..lag-1), G0(lag), G1(0), G0(lag+1), G1(1), ...
-  if (ctl->ok) {
-    for (int t = 1 + tid; t < nLx; t += kThreads)
-      if (tb.lx_mt0[t] * tiles_n0_ >= 2 * static_cast<int>(gridDim.x)) atomicMin(&ctl->lag, t);
-  }
-  __syncthreads();
-  if (ctl->ok) {
+    if (lane == 0) tb.lx_mt0[nLx] = mt;
+    __syncwarp();
+    // task order: GEMM1 of expert i trails GEMM0 of expert i by `lag` experts, the smallest lag
+    // whose GEMM0 tiles cover two tickets per CTA, so that by the time a GEMM1 ticket is drawn the
+    // GEMM0 tiles it depends on are long finished: G0(0..lag-1), G0(lag), G1(0), G0(lag+1), G1(1), ...
+    int lag = nLx;
+    for (int t = 1 + lane; t < nLx; t += 32)
+      if (tb.lx_mt0[t] * tiles_n0_ >= 2 * static_cast<int>(gridDim.x)) { lag = t; break; }
+#pragma unroll
+    for (int off = 16; off >= 1; off >>= 1) lag = min(lag, __shfl_xor_sync(0xffffffffu, lag, off));
     // A ticket is a group of kGroup M tiles (one per CTA of a pair) times one N tile.  Step s of the
     // order emits G0(s) (s < nLx) and then G1(s - lag) (s >= lag); sizes go to seg_first and are
     // turned into first-ticket numbers by the scan below.
-    const int lag = ctl->lag;
-    for (int i = tid; i < nLx; i += kThreads) {
+    for (int i = lane; i < nLx; i += 32) {
       const int groups = (tb.lx_mt0[i + 1] - tb.lx_mt0[i] + kGroup - 1) / kGroup;
       const int i0 = i + max(0, i - lag);                                   // G0(i)
       const int s1 = i + lag;
@@ -670,9 +666,7 @@ __device__ __forceinline__ void moe_forward_body(const MoeParams& p, const TmaMa
       tb.seg_whole[i1] = tiles - cut;
       tb.seg_kind[i1] = kTaskGemm1; tb.seg_lx[i1] = i;
     }
-  }
-  __syncthreads();
-  if (ctl->ok && warp == 0) {
+    __syncwarp();
     const int total = warp_scan([&](int i) { return tb.seg_first[i]; },
                                 [&](int i, int v) { tb.seg_first[i] = v; }, 2 * nLx);
     if (lane == 0) {
@@ -680,9 +674,9 @@ __device__ __forceinline__ void moe_forward_body(const MoeParams& p, const TmaMa
       ctl->n_segs = 2 * nLx;
       ctl->total_tasks = total;
     }
+    __syncwarp();
+    stamp(2);
   }
-  __syncthreads();
-  stamp(2);
 
   // ---- dispatch: push this rank's routed rows to the experts' owners --------------------
   // Done by the four epilogue warps of every CTA, on their way into the epilogue loop; warps 0 and
