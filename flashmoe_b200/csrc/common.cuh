@@ -31,7 +31,7 @@ constexpr int kUmmaN = 256;      // UMMA N: gate|up halves for GEMM0, 256 output
 // TMA -> UMMA ring: 6 stages of 32 KB per CTA in pair mode, 4 stages of 48 KB alone (192 KB both)
 constexpr int kAccBufs = 2;      // TMEM accumulator double buffer (2 x 256 columns)
 constexpr int kTaskSlots = 4;    // task ring between the scheduler warp and its consumers
-constexpr int kThreads = 192;    // warp 0 scheduler + TMA, warp 1 UMMA, warps 2..5 epilogue
+constexpr int kThreads = 256;    // warp 0 scheduler + TMA, warp 1 UMMA, warps 2..5 epilogue (+ dispatch), warps 6..7 dispatch
 constexpr uint32_t kStageABytes = kTileM * kTileK * 2;        // 128 rows x 64 columns of 16-bit: 16 KB
 
 constexpr int kTraceSlots = 16;   // phase stamps per CTA

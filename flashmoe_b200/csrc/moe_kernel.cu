@@ -21,9 +21,10 @@
 //    deadlock as long as all CTAs are co-resident (grid <= SM count, one CTA per SM), which the
 //    cooperative launch guarantees.
 //  * Each CTA is warp-specialised: warp 0 = scheduler + TMA producer, warp 1 = UMMA issuer and
-//    TMEM owner, warps 2..5 = dispatch and epilogue: they push this rank's routed rows to the
-//    experts' owners in batches, between epilogues, while warps 0 and 1 already work on the
-//    first tiles whose rows are in.  By default every CTA works alone on 128 x 256 output
+//    TMEM owner, warps 2..5 = epilogue, warps 6..7 = dispatch: this rank's routed rows go to the
+//    experts' owners in chunks taken from a per-CTA queue by the dispatch warps and, between
+//    epilogues, by the epilogue warps, while warps 0 and 1 already work on the first tiles whose
+//    rows are in.  By default every CTA works alone on 128 x 256 output
 //    tiles (tcgen05.mma.cta_group::1, M = 128, N = 256): a 4-stage TMA->UMMA ring of 48 KB stages
 //    (A tile 128 x 64, B tile 256 x 64) and a double-buffered 2 x 256-column TMEM accumulator
 //    overlap loads, MMA and epilogue.  A second form of the same body (opt-in) runs CTA pairs,
@@ -97,6 +98,7 @@ struct Control {
   uint32_t tmem_base;
   uint32_t ok;            // cleared when a CTA-wide wait failed
   int total_tasks, n_segs, send_rows, class0_experts, expected_ret, lag;
+  int next_chunk;          // dispatch: next chunk of this CTA's rows nobody has taken yet
   uint64_t epoch;
 };
 
@@ -322,6 +324,7 @@ __device__ __forceinline__ void moe_forward_body(const MoeParams& p, const TmaMa
       mbar_init(&ctl->pair_full[i], 1); mbar_init(&ctl->pair_empty[i], 1);
     }
     ctl->ok = 1;
+    ctl->next_chunk = kThreads / 32 - 2;   // every dispatching warp starts on the chunk of its own number
     ctl->epoch = *p.epoch;
     mbar_fence_init();
     prefetch_tmap(&maps.landing); prefetch_tmap(&maps.y); prefetch_tmap(&maps.up);
@@ -552,37 +555,54 @@ __device__ __forceinline__ void moe_forward_body(const MoeParams& p, const TmaMa
   // k choices.  Lane i of a dispatching warp looks up row (q + i): the dependent loads (routing
   // table, then the token's route records) are in flight before the counts of the peers are in.
   struct RowInfo { int pos, row; uint32_t token, choice; };
-  // This warp's share of the rows to send (epilogue warps): its slice of class 0 followed by its
-  // slice of class 1, as one list; entry v of the list is row a0 + v, or a1 + (v - n0).
-  int a0 = 0, n0 = 0, a1 = 0, n1 = 0;
-  auto lookup = [&](int v0) -> RowInfo {      // lane i looks up list entry v0 + i
+  // This CTA's share of the rows to send: a contiguous slice of class 0 and one of class 1, cut
+  // into chunks of `chunk_rows` rows (at most 16) that the CTA's dispatching warps take from a
+  // queue: warps 6 and 7 do nothing else, the epilogue warps 2..5 take chunks whenever no finished
+  // accumulator is waiting for them.  Class 0 chunks come first in the queue.
+  int cta_a0 = 0, cta_n0 = 0, cta_a1 = 0, cta_n1 = 0, chunk_rows = 1, chunks0 = 0, total_chunks = 0;
+  {
+    const long long R0 = tb.send_pref[ctl->class0_experts], R1 = ctl->send_rows - R0;
+    const long long nc = gridDim.x, c = blockIdx.x;
+    cta_a0 = static_cast<int>(R0 * c / nc); cta_n0 = static_cast<int>(R0 * (c + 1) / nc) - cta_a0;
+    cta_a1 = static_cast<int>(R0 + R1 * c / nc); cta_n1 = static_cast<int>(R0 + R1 * (c + 1) / nc) - cta_a1;
+    constexpr int kDispWarps = kThreads / 32 - 2;
+    chunk_rows = min(16, max(1, (cta_n0 + cta_n1 + kDispWarps - 1) / kDispWarps));
+    chunks0 = (cta_n0 + chunk_rows - 1) / chunk_rows;
+    total_chunks = chunks0 + (cta_n1 + chunk_rows - 1) / chunk_rows;
+  }
+  auto chunk_range = [&](int ch, int& first, int& len) {
+    if (ch < chunks0) { first = cta_a0 + ch * chunk_rows; len = min(chunk_rows, cta_a0 + cta_n0 - first); }
+    else { first = cta_a1 + (ch - chunks0) * chunk_rows; len = min(chunk_rows, cta_a1 + cta_n1 - first); }
+  };
+  auto lookup = [&](int ch) -> RowInfo {      // lane i looks up row i of chunk ch
     RowInfo ri{0, 0, 0u, 0u};
-    const int v = v0 + lane;
-    if (v < n0 + n1) {
-      const int row = v < n0 ? a0 + v : a1 + (v - n0);
-      int lo = 0, hi = E;  // largest position with send_pref[position] <= row
-      while (hi - lo > 1) {
-        const int mid = (lo + hi) >> 1;
-        if (tb.send_pref[mid] <= row) lo = mid; else hi = mid;
+    if (ch < total_chunks) {
+      int first, len;
+      chunk_range(ch, first, len);
+      if (lane < len) {
+        const int row = first + lane;
+        int lo = 0, hi = E;  // largest position with send_pref[position] <= row
+        while (hi - lo > 1) {
+          const int mid = (lo + hi) >> 1;
+          if (tb.send_pref[mid] <= row) lo = mid; else hi = mid;
+        }
+        const int e = tb.ord[lo];
+        ri.pos = lo;
+        ri.row = row;
+        ri.token = p.table[static_cast<size_t>(e) * p.round_ec + (row - tb.send_pref[lo])].token;
+        for (int c = 0; c < K_; ++c)
+          if (p.routes[static_cast<size_t>(ri.token) * K_ + c].expert == e) { ri.choice = c; break; }
       }
-      const int e = tb.ord[lo];
-      ri.pos = lo;
-      ri.row = row;
-      ri.token = p.table[static_cast<size_t>(e) * p.round_ec + (row - tb.send_pref[lo])].token;
-      for (int c = 0; c < K_; ++c)
-        if (p.routes[static_cast<size_t>(ri.token) * K_ + c].expert == e) { ri.choice = c; break; }
     }
     return ri;
   };
-  RowInfo pre{0, 0, 0u, 0u};
-  if (warp >= 2) {
-    const int G = gridDim.x * 4;
-    const int gw = blockIdx.x * 4 + (warp - 2);
-    const long long R0 = tb.send_pref[ctl->class0_experts], R1 = ctl->send_rows - R0;
-    a0 = static_cast<int>(R0 * gw / G); n0 = static_cast<int>(R0 * (gw + 1) / G) - a0;
-    a1 = static_cast<int>(R0 + R1 * gw / G); n1 = static_cast<int>(R0 + R1 * (gw + 1) / G) - a1;
-    pre = lookup(0);
-  }
+  auto next_chunk = [&]() -> int {            // the next chunk nobody has taken (warp-uniform)
+    int ch = 0;
+    if (lane == 0) ch = atomicAdd(&ctl->next_chunk, 1);
+    return __shfl_sync(0xffffffffu, ch, 0);
+  };
+  int my_chunk = warp >= 2 ? warp - 2 : total_chunks;
+  RowInfo pre = lookup(my_chunk);             // in flight while the peers' counts travel
 
   if (tid < W) {
     const uint64_t* f = reinterpret_cast<const uint64_t*>(self + p.lay.cnt_flag) + parity * W + tid;
@@ -683,8 +703,7 @@ __device__ __forceinline__ void moe_forward_body(const MoeParams& p, const TmaMa
   // 1 are already drawing tickets and loading weights.  A GEMM0 ticket waits for the rows of its
   // own M tile only (per source, on disp_arrived) and the dispatch depends on no ticket, so the
   // order stays deadlock-free; the first epilogue is due one whole main loop after the first MMA.
-  // Sends the list entries [w0 + a, w0 + b) of the 32-entry window that starts at w0; `ri` holds
-  // the window's look-ups (lane i = entry w0 + i).
+  // Sends the rows [a, b) of a chunk; `ri` holds the chunk's look-ups (lane i = row i of the chunk).
   auto send_rows = [&](const int a, const int b, const RowInfo ri) {
     const int vecs = H_ * EB / 16;
     const uint4* tok_base = static_cast<const uint4*>(p.tokens);
@@ -971,22 +990,30 @@ __device__ __forceinline__ void moe_forward_body(const MoeParams& p, const TmaMa
         ++acc_it;
       }
     }
+  } else if (ctl->ok && warp >= 6) {
+    // dispatch warps: chunks of this CTA's rows until the queue is empty
+    RowInfo cur = pre;
+    while (my_chunk < total_chunks) {
+      int first, len;
+      chunk_range(my_chunk, first, len);
+      send_rows(0, len, cur);
+      my_chunk = next_chunk();
+      cur = lookup(my_chunk);
+    }
+    if (warp == 6 && lane == 0) stamp_now(3);
   } else if (ctl->ok) {
     // epilogue warps: TMEM lane quadrant = warp id mod 4; this CTA's 128 rows of the pair's tile.
-    // They also carry the dispatch: rows are sent in batches of 16 for as long as no finished
-    // accumulator is waiting for them, so a long dispatch (many routed rows per warp) never keeps
-    // the MMA warp waiting for a free TMEM buffer.
+    // They help with the dispatch for as long as no finished accumulator is waiting for them, so
+    // the first rows leave on six warps per CTA and a long dispatch (many routed rows per CTA)
+    // never keeps the MMA warp waiting for a free TMEM buffer.
     const int quad = warp & 3;
     const int row_in_tile = quad * 32 + lane;
     uint32_t acc_empty_leader = 0;
     if constexpr (kPair) acc_empty_leader = map_to_cta(&ctl->acc_empty[0], 0);
     uint32_t tslot = 0, acc_it = 0;
-    const int nsend = n0 + n1;
-    int sent = 0;
-    RowInfo win = pre;               // look-ups of the window [sent & ~31, +32)
-    if (nsend == 0 && warp == 2 && lane == 0) stamp_now(3);
+    RowInfo cur = pre;               // look-ups of the chunk this warp holds (my_chunk)
     for (uint32_t it = 0;; ++it, tslot = (tslot + 1) % kTaskSlots) {
-      while (sent < nsend) {
+      while (my_chunk < total_chunks) {
         // lane 0 looks: is the next task known, and (unless it is the stop task) its accumulator full?
         int ready = 0;
         if (lane == 0 && mbar_try_wait(&ctl->task_full[tslot], (it / kTaskSlots) & 1)) {
@@ -995,12 +1022,11 @@ __device__ __forceinline__ void moe_forward_body(const MoeParams& p, const TmaMa
                   mbar_try_wait_cluster(&ctl->acc_full[b], (acc_it / kBufs) & 1);
         }
         if (__shfl_sync(0xffffffffu, ready, 0)) break;
-        const int w0 = sent & ~31;
-        const int upto = min(min(sent + 16, w0 + 32), nsend);
-        send_rows(sent - w0, upto - w0, win);
-        sent = upto;
-        if (sent < nsend && (sent & 31) == 0) win = lookup(sent);
-        if (sent == nsend && warp == 2 && lane == 0) stamp_now(3);
+        int first, len;
+        chunk_range(my_chunk, first, len);
+        send_rows(0, len, cur);
+        my_chunk = next_chunk();
+        cur = lookup(my_chunk);
       }
       if (!mbar_wait(&ctl->task_full[tslot], (it / kTaskSlots) & 1, wc)) {
         fail(p, FMOE_PHASE_TASK, -2); break;

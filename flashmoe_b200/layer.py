@@ -158,14 +158,18 @@ class MoELayer:
         and the share of the kernel a median CTA spent in communication it could not overlap:
         the count exchange, the wait of its first task for dispatched rows (tables built -> first
         operand tiles landed) and the wait, after its own last task, for returned rows.  The
-        dispatch itself runs on the epilogue warps while the other warps are in the GEMM loop."""
+        dispatch itself ("dispatch": all counts in -> this CTA's dispatch warps done) runs beside
+        the GEMM loop."""
         g = self.geometry()
         t = self.debug(5, torch.int64, (g.grid, 16)).cpu().double()
         d = (t[:, 1:8] - t[:, 0:7]) / 1e3
         med = d.median(dim=0).values
         first = t[:, 8] > 0                      # CTAs that issued MMAs at all
         first_mma = float(((t[first, 8] - t[first, 2]) / 1e3).median()) if bool(first.any()) else 0.0
-        out = {"count_exchange": float(med[0]), "tables": float(med[1]), "dispatch": float(med[2]),
+        # the dispatch warps start as soon as the landing rows are known, while warp 0 still builds
+        # the task order: their time is counted from the moment all counts were in
+        out = {"count_exchange": float(med[0]), "tables": float(med[1]),
+               "dispatch": float(((t[:, 3] - t[:, 1]) / 1e3).median()),
                "first_rows_wait": first_mma,
                "gemm_tickets": float(((t[:, 4] - t[:, 2]) / 1e3).median()),
                "drain_last_task": float(med[4]),

@@ -276,8 +276,8 @@ int fmoe_get_geometry(const fmoe_ctx* ctx, fmoe_geometry* out);
  *        2 GEMM0 output [landing_rows, I], 3 return rows [S*k, H],
  *        4 route records [S, k] of {int32 expert, int32 slot, float weight},
  *        5 phase stamps of the last forward: uint64 [grid][16] %globaltimer nanoseconds per CTA
- *          (0 start, 1 all ranks' counts in, 2 tables built, 3 this CTA's share of the dispatch
- *           done, 4 last ticket drawn, 5 this CTA's last task finished, 6 all returns in,
+ *          (0 start, 1 all ranks' counts in, 2 task order built (warp 0), 3 this CTA's dispatch
+ *           warps done (may precede 2), 4 last ticket drawn, 5 this CTA's last task finished, 6 all returns in,
  *           7 combine done, 8 first operand tiles of the CTA's first task landed (0: it had none),
  *           9, 10, 11 the epilogue of the CTA's last task: accumulator ready, rows stored, owners
  *           told; 12..15 unused) */
