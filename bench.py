@@ -401,6 +401,7 @@ def short_measure(name, tokens, world, rank, local_rank, dev, dist, peaks, peaks
             oks = [None] * world
             dist.all_gather_object(oks, par["ok"])
         res = {"workload": f"{name}@{w.tokens_per_rank}", "dtype": w.data_type.name.lower(),
+               "specialised_kernel": bool(layer.geometry().specialised),
                "fwd_us": fwd_us, "router_us": router_us, "step_as_one_launch_us": one_launch_us,
                "tokens_per_s": w.tokens_per_rank * world / ((fwd_us + router_us) * 1e-6),
                "bound": roof["bound"], "frac": roof["frac"],
@@ -651,6 +652,9 @@ def main() -> int:
         return float(t.item())
 
     st = layer.stream
+    # true when the forward runs the kernel compiled for this layer's description (built ahead of
+    # time into flashmoe_b200/lib/spec by __graft_entry__.build(); the generic kernel otherwise)
+    specialised = bool(layer.geometry().specialised)
     with torch.cuda.stream(st):
         for _ in range(a.warmup):
             layer.step()
@@ -855,7 +859,7 @@ def main() -> int:
                     "ms_per_step_one_at_a_time": e2e_sync_s * 1e3, "host_link": pcie,
                     "api": "fmoe_forward_host_async + fmoe_forward_host_wait (C ABI, pinned host buffers; "
                            "copies of neighbouring steps overlap the kernels)"},
-            "gpu_launches": int(launches), "parity": parity, "phases_us": phases, "nvlink": nvlink,
+            "gpu_launches": int(launches), "specialised_kernel": specialised, "parity": parity, "phases_us": phases, "nvlink": nvlink,
             "roofline": roofline, "cpu_baseline": cpu, "clocks": clocks, "vs_unfused": vs_unfused,
             "other_workloads": others}
     if a.proxy_ep:

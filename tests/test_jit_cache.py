@@ -66,3 +66,17 @@ def test_two_processes_race_for_one_artefact(tmp_path):
     assert lib.fmoe_spec_info(info) == 0
     assert list(info)[:7] == [320, 384, 2, 1, 1, 0, 0]
     assert hasattr(lib, "fmoe_spec_prepare") and hasattr(lib, "fmoe_spec_launch")
+
+
+@needs_nvcc
+def test_benchmark_shapes_have_their_specialised_kernels_after_build():
+    """`__graft_entry__.build()` leaves a library for every benchmark description in the in-tree
+    cache, keyed by the CURRENT sources: a stale cache (sources edited, build not re-run) would
+    silently put the benchmark on the generic kernel."""
+    import __graft_entry__ as entry
+    from flashmoe_b200.workloads import CONFIGS
+    entry.build_specialised()
+    for w in CONFIGS.values():
+        a = flashmoe.InitArgs(w.data_type, w.tokens_per_rank, w.token_dim, w.ffn_size, w.num_experts, w.top_k,
+                              1000, w.mlp_type, w.act_type, 0, 0)
+        assert jit.specialised_library(a, build=False) is not None, w.name
