@@ -97,7 +97,7 @@ struct Control {
   Task tasks[kTaskSlots];
   uint32_t tmem_base;
   uint32_t ok;            // cleared when a CTA-wide wait failed
-  int total_tasks, n_segs, send_rows, class0_experts, expected_ret, lag;
+  int total_tasks, n_segs, send_rows, class0_experts, expected_ret;
   int next_chunk;          // dispatch: next chunk of this CTA's rows nobody has taken yet
   uint64_t epoch;
 };
@@ -338,10 +338,10 @@ __device__ __forceinline__ void moe_forward_body(const MoeParams& p, const TmaMa
   __syncthreads();
   if constexpr (kPair) cluster_sync_all();   // the peer's barriers exist before anything arrives on them
   tc_fence_after_sync();
-  // per-CTA phase stamps (%globaltimer, ns): 0 start, 1 counts of all ranks in, 2 tables built,
-  // 3 this CTA's share of the dispatch done (its epilogue warps; the other warps are already in the
-  // GEMM loop), 4 last ticket (stop) drawn, 5 this CTA's last task finished, 6 returns all in,
-  // 7 combine done, 8 first operand stage of this CTA's first task landed (the first MMA can issue)
+  // per-CTA phase stamps (%globaltimer, ns): 0 start, 1 counts of all ranks in, 2 task order built
+  // (warp 0), 3 this CTA's dispatch warps done (may precede 2), 4 last ticket (stop) drawn, 5 this
+  // CTA's last task finished, 6 returns all in, 7 combine done, 8 first operand stage of this CTA's
+  // first task landed (the first MMA can issue), 9..11 the epilogue of the CTA's last task
   auto stamp_now = [&](int i) {   // called by one thread
     unsigned long long t;
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
@@ -699,10 +699,10 @@ __device__ __forceinline__ void moe_forward_body(const MoeParams& p, const TmaMa
   }
 
   // ---- dispatch: push this rank's routed rows to the experts' owners --------------------
-  // Done by the four epilogue warps of every CTA, on their way into the epilogue loop; warps 0 and
-  // 1 are already drawing tickets and loading weights.  A GEMM0 ticket waits for the rows of its
-  // own M tile only (per source, on disp_arrived) and the dispatch depends on no ticket, so the
-  // order stays deadlock-free; the first epilogue is due one whole main loop after the first MMA.
+  // Done by warps 6 and 7 of every CTA and, between epilogues, by the epilogue warps; warps 0 and 1
+  // are already drawing tickets and loading weights.  A GEMM0 ticket waits for the rows of its own
+  // M tile only (per source, on disp_arrived) and the dispatch depends on no ticket, so the order
+  // stays deadlock-free.
   // Sends the rows [a, b) of a chunk; `ri` holds the chunk's look-ups (lane i = row i of the chunk).
   auto send_rows = [&](const int a, const int b, const RowInfo ri) {
     const int vecs = H_ * EB / 16;
