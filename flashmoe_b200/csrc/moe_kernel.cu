@@ -39,7 +39,7 @@
 //    is rounded to Element, the product is rounded to Element, the GEMM1 output is rounded
 //    to Element.
 //  * Expert outputs return to the token's owner as rows indexed by (token, choice), written as
-//    whole 64/128-byte runs of one row through a shared-memory transpose; the owner sums a
+//    whole 128-byte runs of one row through a shared-memory transpose; the owner sums a
 //    token's k rows in fp32 in selection order and rounds once (the reference accumulates with
 //    Element-precision atomics in arrival order, combine.cuh:120-223).
 //  * The last GEMM1 tiles of the task order are cut along K into parts whose fp32 partial sums
@@ -1178,9 +1178,9 @@ __device__ __forceinline__ void moe_forward_body(const MoeParams& p, const TmaMa
           // Bias, rounding, and the row's 32 columns on their way to the token's owner.  A lane holds
           // 32 columns of ITS row, so a warp-wide store straight from registers would be 32 pieces of
           // 16 bytes in 32 different rows, which is the worst shape for a write that may cross
-          // NVLink.  The chunk is transposed through 2 KB of shared memory instead (16-byte pieces,
-          // xor-swizzled against bank conflicts) and leaves as 64-byte (16-bit types: 8 rows per
-          // instruction) or 128-byte (fp32: 4 rows per instruction) runs of one row each.
+          // NVLink.  128 bytes of every row (two chunks of a 16-bit type, one of fp32) are transposed
+          // through 2 KB of shared memory instead (16-byte pieces, xor-swizzled against bank
+          // conflicts) and leave as 128-byte runs of one row each, four rows per instruction.
           uint4* stage_w = ret_stage + (warp - 2) * 128;
           const uint32_t orow_lo = static_cast<uint32_t>(reinterpret_cast<uintptr_t>(orow));
           const uint32_t orow_hi = static_cast<uint32_t>(reinterpret_cast<uintptr_t>(orow) >> 32);
@@ -1188,53 +1188,54 @@ __device__ __forceinline__ void moe_forward_body(const MoeParams& p, const TmaMa
             const uint32_t lo = __shfl_sync(0xffffffffu, orow_lo, r), hi = __shfl_sync(0xffffffffu, orow_hi, r);
             return reinterpret_cast<char*>((static_cast<uintptr_t>(hi) << 32) | lo);
           };
-          auto finish_chunk = [&](int c, float (&o)[32]) {   // every lane of the warp calls this
+          // 128 bytes of every row of the warp (32 words per lane) out through the 2 KB stage, 16
+          // rows at a time: every store instruction writes four whole 128-byte runs.
+          auto stage_out = [&](const uint32_t (&w)[32], size_t byte_off) {
+#pragma unroll
+            for (int pass = 0; pass < 2; ++pass) {
+              if ((lane >> 4) == pass) {
+                const int r16 = lane & 15;
+                uint4* mine = stage_w + r16 * 8;
+#pragma unroll
+                for (int q = 0; q < 8; ++q)
+                  mine[q ^ (r16 & 7)] = make_uint4(w[4 * q], w[4 * q + 1], w[4 * q + 2], w[4 * q + 3]);
+              }
+              __syncwarp();
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                const int r16 = 4 * i + (lane >> 3), piece = lane & 7, r = pass * 16 + r16;
+                const uint4 v = stage_w[r16 * 8 + (piece ^ (r16 & 7))];
+                char* dst = row_ptr(r);
+                const bool ok = __shfl_sync(0xffffffffu, valid ? 1 : 0, r) != 0;
+                if (ok) *reinterpret_cast<uint4*>(dst + byte_off + piece * 16) = v;
+              }
+              __syncwarp();
+            }
+          };
+          uint32_t held[16];   // 16-bit types: the even chunk of a pair waits here for the odd one
+          auto finish_chunk = [&](int c, float (&o)[32]) {   // every lane of the warp calls this, c ascending
             const int col0 = col_base + c * 32;
-            if (col0 >= H_) return;
+            if (col0 >= H_) return;                            // H is a multiple of 64: whole pairs
             if (valid) {
 #pragma unroll
               for (int i = 0; i < 32; ++i)
                 o[i] += bias_at<T>(p.bias_down, static_cast<size_t>(t.lx) * H_ + col0 + i);
             }
             if constexpr (EB == 2) {
-              uint4* mine = stage_w + lane * 4;
-              const int sw = (lane >> 1) & 3;
+              if ((c & 1) == 0) {
 #pragma unroll
-              for (int q = 0; q < 4; ++q)
-                mine[q ^ sw] = make_uint4(Cvt<T>::pack(o[8 * q], o[8 * q + 1]), Cvt<T>::pack(o[8 * q + 2], o[8 * q + 3]),
-                                          Cvt<T>::pack(o[8 * q + 4], o[8 * q + 5]), Cvt<T>::pack(o[8 * q + 6], o[8 * q + 7]));
-              __syncwarp();
+                for (int i = 0; i < 16; ++i) held[i] = Cvt<T>::pack(o[2 * i], o[2 * i + 1]);
+              } else {
+                uint32_t w[32];
 #pragma unroll
-              for (int i = 0; i < 4; ++i) {
-                const int r = 8 * i + (lane >> 2), piece = lane & 3;
-                const uint4 v = stage_w[r * 4 + (piece ^ ((r >> 1) & 3))];
-                char* dst = row_ptr(r);
-                const bool ok = __shfl_sync(0xffffffffu, valid ? 1 : 0, r) != 0;
-                if (ok) *reinterpret_cast<uint4*>(dst + static_cast<size_t>(col0) * 2 + piece * 16) = v;
+                for (int i = 0; i < 16; ++i) { w[i] = held[i]; w[16 + i] = Cvt<T>::pack(o[2 * i], o[2 * i + 1]); }
+                stage_out(w, static_cast<size_t>(col0 - 32) * 2);
               }
-              __syncwarp();
             } else {
+              uint32_t w[32];
 #pragma unroll
-              for (int pass = 0; pass < 2; ++pass) {
-                if ((lane >> 4) == pass) {
-                  const int r16 = lane & 15;
-                  uint4* mine = stage_w + r16 * 8;
-#pragma unroll
-                  for (int q = 0; q < 8; ++q)
-                    mine[q ^ (r16 & 7)] = make_uint4(__float_as_uint(o[4 * q]), __float_as_uint(o[4 * q + 1]),
-                                                     __float_as_uint(o[4 * q + 2]), __float_as_uint(o[4 * q + 3]));
-                }
-                __syncwarp();
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                  const int r16 = 4 * i + (lane >> 3), piece = lane & 7, r = pass * 16 + r16;
-                  const uint4 v = stage_w[r16 * 8 + (piece ^ (r16 & 7))];
-                  char* dst = row_ptr(r);
-                  const bool ok = __shfl_sync(0xffffffffu, valid ? 1 : 0, r) != 0;
-                  if (ok) *reinterpret_cast<uint4*>(dst + static_cast<size_t>(col0) * 4 + piece * 16) = v;
-                }
-                __syncwarp();
-              }
+              for (int i = 0; i < 32; ++i) w[i] = __float_as_uint(o[i]);
+              stage_out(w, static_cast<size_t>(col0) * 4);
             }
           };
           if (!split) {
