@@ -508,6 +508,25 @@ int fmoe_symm_export(fmoe_ctx* ctx, void* handle_out) {
   if (ctx == nullptr || handle_out == nullptr) return set_error(FMOE_ERR_INVALID_ARG, "null argument");
   static_assert(sizeof(cudaIpcMemHandle_t) == FMOE_IPC_HANDLE_BYTES, "IPC handle size");
   FMOE_CUDA(cudaSetDevice(ctx->device));
+  if (!ctx->owns_memory) {
+    // CUDA IPC shares whole allocations: a peer that opens the handle gets the allocation's first
+    // byte, so a caller's block that starts anywhere else would be mapped at the wrong address.
+    typedef CUresult (*RangeFn)(CUdeviceptr*, size_t*, CUdeviceptr);
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuMemGetAddressRange", &sym, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess && sym != nullptr) {
+      CUdeviceptr base = 0;
+      size_t size = 0;
+      if (reinterpret_cast<RangeFn>(sym)(&base, &size, reinterpret_cast<CUdeviceptr>(ctx->symm)) == CUDA_SUCCESS &&
+          base != reinterpret_cast<CUdeviceptr>(ctx->symm))
+        return set_error(FMOE_ERR_INVALID_ARG,
+                         "the caller's symmetric block starts " +
+                             std::to_string(reinterpret_cast<CUdeviceptr>(ctx->symm) - base) +
+                             " bytes into its device allocation; to be shared through CUDA IPC it must be an "
+                             "allocation of its own (or map the peers yourself and use fmoe_symm_set_peer)");
+    }
+  }
   cudaIpcMemHandle_t h;
   FMOE_CUDA(cudaIpcGetMemHandle(&h, ctx->symm));
   std::memcpy(handle_out, &h, sizeof(h));
