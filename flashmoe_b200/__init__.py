@@ -129,6 +129,9 @@ def initialize(arg: InitArgs, memory=None) -> ContextHandle:
 
     `memory` = (symmetric address, bytes, workspace address, bytes) places the context in device
     memory the caller owns (sizes from `get_workspace_bytes`); by default the library allocates.
+    With more than one rank the symmetric part must be a device allocation of its own, not a
+    slice of a larger one (a tensor of torch's caching allocator usually is a slice): CUDA IPC
+    maps whole allocations, and the export refuses anything else.
 
     With `ep_rank` unset the group is taken from the communication bootstrap and experts are
     blocked over the ranks (`expert_map[i] = i // num_local_experts`); the fields are written
