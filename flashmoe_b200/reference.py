@@ -25,8 +25,8 @@ class RefForwardArgs:
     ref_interim1 [*, H]; ref_out [S, H]."""
 
     def __init__(self, expert_up: int, expert_down: int, bias_up: int, bias_down: int, ref_input: int,
-                 ref_interim0: int, ref_interim1: int, ref_out: int, *, expert_up_v: int = 0,
-                 bias_up_v: int = 0):
+                 ref_interim0: int, ref_interim1: int, ref_out: int, *, expert_up_v: int,
+                 bias_up_v: int):
         self.ref_input = ref_input
         self.ref_interim0 = ref_interim0
         self.ref_interim1 = ref_interim1

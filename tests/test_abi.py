@@ -126,6 +126,82 @@ def test_python_api_surface_matches_the_reference():
             r.ref_out, r.expert_up_v, r.bias_up_v) == (1, 2, 3, 4, 5, 6, 7, 8, 9, 10)
 
 
+def _params(fn):
+    import inspect
+    out = []
+    for q in inspect.signature(fn).parameters.values():
+        if q.name != "self":
+            out.append({"name": q.name, "kind": q.kind.name,
+                        "default": None if q.default is inspect.Parameter.empty else repr(q.default),
+                        "required": q.default is inspect.Parameter.empty})
+    return out
+
+
+def _holds(ours, theirs, where):
+    """Every parameter of the reference's callable is here under the same name, at the same position
+    among the positional ones, of the same kind and with the same default; what this package adds
+    must be optional, so that a call written for the reference means the same thing here."""
+    ours_by = {q["name"]: q for q in ours}
+    for q in theirs:
+        assert q["name"] in ours_by, f"{where}: parameter {q['name']} is missing"
+        mine = ours_by[q["name"]]
+        assert (mine["kind"], mine["default"], mine["required"]) == (q["kind"], q["default"], q["required"]), \
+            f"{where}: {q['name']} is {mine}, the reference has {q}"
+    positional = lambda ps: [q["name"] for q in ps if q["kind"] in ("POSITIONAL_ONLY", "POSITIONAL_OR_KEYWORD")]
+    assert positional(ours)[:len(positional(theirs))] == positional(theirs), f"{where}: positional order differs"
+    for q in ours:
+        if q["name"] not in {t["name"] for t in theirs}:
+            assert not q["required"], f"{where}: added parameter {q['name']} must be optional"
+
+
+def test_python_api_follows_the_surface_recorded_from_the_reference():
+    """tests/golden/api_surface.json was written by tests/golden/make_api_surface.py from the
+    reference's own modules (flashmoe/__init__.py, jit.py, router.py, reference.py, cb.py)."""
+    import json
+    from enum import IntEnum
+    surface = json.load(open(os.path.join(ROOT, "tests", "golden", "api_surface.json")))
+    for name in surface["package_names"]:
+        assert hasattr(flashmoe, name), f"flashmoe.{name} is missing"
+    modules = {"flashmoe": flashmoe, "flashmoe.router": flashmoe.router, "flashmoe.reference": flashmoe.reference,
+               "flashmoe.cb": flashmoe.cb}
+    for mod_name, fns in surface["functions"].items():
+        for fn_name, theirs in fns.items():
+            fn = getattr(modules[mod_name], fn_name, None)
+            assert callable(fn), f"{mod_name}.{fn_name} is missing"
+            _holds(_params(fn), theirs, f"{mod_name}.{fn_name}")
+    for enum_name, members in surface["enums"].items():
+        ours = getattr(flashmoe, enum_name)
+        assert {m.name: int(m) for m in ours} == members
+    classes = {"InitArgs": flashmoe.InitArgs, "ForwardArgs": flashmoe.ForwardArgs,
+               "RouterForwardArgs": flashmoe.router.RouterForwardArgs,
+               "RefForwardArgs": flashmoe.reference.RefForwardArgs, "ContextHandle": flashmoe.ContextHandle}
+    for cls_name, theirs in surface["constructors"].items():
+        _holds(_params(classes[cls_name].__init__), theirs, f"{cls_name}()")
+    # the same constructor calls leave the same values in the same fields
+    D, M, A = flashmoe.DataType, flashmoe.MLPType, flashmoe.ActivationType
+    made = {
+        "InitArgs": flashmoe.InitArgs(D.BF16, 1024, 5120, 8192, 16, 1, 1000, M.GATED, A.SILU, 11, 3),
+        "ForwardArgs": flashmoe.ForwardArgs(M.VANILLA, 1, 2, 3, 4, 5, 6, 7, 8),
+        "RouterForwardArgs": flashmoe.router.RouterForwardArgs(1, 2, 3, 4),
+        "RefForwardArgs": flashmoe.reference.RefForwardArgs(1, 2, 3, 4, 5, 6, 7, 8, expert_up_v=9, bias_up_v=10),
+    }
+    for cls_name, fields in surface["fields"].items():
+        for field, value in fields.items():
+            got = getattr(made[cls_name], field)
+            got = int(got) if isinstance(got, IntEnum) else got
+            assert got == value, f"{cls_name}.{field}: {got!r}, the reference leaves {value!r}"
+    for prop in surface["context_handle_properties"]:
+        assert isinstance(getattr(flashmoe.ContextHandle, prop), property)
+    for s, e, k, cap in surface["derived_capacity"]:
+        a = flashmoe.InitArgs(D.BF16, s, 64, 64, e, k, 1000, M.GATED, A.SILU, 0, 0)
+        assert a.expert_peer_capacity == cap, (s, e, k)
+    assert surface["asserts"]["gated_forward_args_need_up_v"] and surface["asserts"]["gpu_arch_below_700"]
+    with pytest.raises(AssertionError):
+        flashmoe.ForwardArgs(M.GATED, 1, 2, 3, 4, 5, 6, 7, 8)
+    with pytest.raises(AssertionError):
+        flashmoe.InitArgs(D.BF16, 8, 64, 64, 8, 1, 600, 0, 0, 0, 0)
+
+
 def test_initialize_without_a_gpu_fails_loudly():
     import torch
     if torch.cuda.is_available():
