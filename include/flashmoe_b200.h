@@ -215,7 +215,7 @@ int fmoe_router_destroy(fmoe_router* router, void* stream);
  * is the [num_experts, round_ec] table of {uint32 token, float weight} (round_ec >=
  * expert_peer_capacity), `routes` the [tokens_per_rank, top_k] records of {int32 expert, int32
  * slot, float weight, int32 pad}, 16-byte aligned.  The first call on a device looks up the
- * array's device address; make that call before any stream capture begins.  All calls on a device
+ * array's device address, once.  All calls on a device
  * share the one array: it keeps the last call's contents (nothing in it has to start at zero), and
  * two calls whose kernels overlap on the GPU (different streams, no ordering between them) race on
  * it, so order them. */
