@@ -36,6 +36,23 @@ namespace {
 
 size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
+// Makes `device` current for the rest of the scope and puts the calling thread's device back on
+// every way out: a library called between a host engine's own launches must not leave the engine
+// on another GPU.
+struct ScopedDevice {
+  int prev = -1;
+  cudaError_t err = cudaSuccess;
+  explicit ScopedDevice(int device) {
+    int cur = -1;
+    if (cudaGetDevice(&cur) != cudaSuccess) cur = -1;
+    err = cudaSetDevice(device);
+    if (err == cudaSuccess && cur >= 0 && cur != device) prev = cur;
+  }
+  ~ScopedDevice() { if (prev >= 0) cudaSetDevice(prev); }
+  ScopedDevice(const ScopedDevice&) = delete;
+  ScopedDevice& operator=(const ScopedDevice&) = delete;
+};
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
                                   const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
                                   const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
@@ -359,7 +376,8 @@ static int ctx_create_impl(const fmoe_model_desc* model, const fmoe_ep_desc* ep,
     ++fill[r];
   }
 
-  cudaError_t ce = cudaSetDevice(c->device);
+  ScopedDevice on_device(c->device);
+  cudaError_t ce = on_device.err;
   if (ce != cudaSuccess) { free_ctx(c); return set_error(FMOE_ERR_CUDA, std::string("cudaSetDevice: ") + cudaGetErrorString(ce)); }
   int sms = 0, cc_major = 0;
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, c->device);
@@ -507,7 +525,8 @@ int fmoe_symm_bytes(const fmoe_ctx* ctx, size_t* bytes) {
 int fmoe_symm_export(fmoe_ctx* ctx, void* handle_out) {
   if (ctx == nullptr || handle_out == nullptr) return set_error(FMOE_ERR_INVALID_ARG, "null argument");
   static_assert(sizeof(cudaIpcMemHandle_t) == FMOE_IPC_HANDLE_BYTES, "IPC handle size");
-  FMOE_CUDA(cudaSetDevice(ctx->device));
+  ScopedDevice on_device(ctx->device);
+  FMOE_CUDA(on_device.err);
   if (!ctx->owns_memory) {
     // CUDA IPC shares whole allocations: a peer that opens the handle gets the allocation's first
     // byte, so a caller's block that starts anywhere else would be mapped at the wrong address.
@@ -537,7 +556,8 @@ int fmoe_symm_import(fmoe_ctx* ctx, int32_t peer, const void* handle) {
   if (ctx == nullptr || handle == nullptr) return set_error(FMOE_ERR_INVALID_ARG, "null argument");
   if (peer < 0 || peer >= ctx->W) return set_error(FMOE_ERR_INVALID_ARG, "peer rank out of range");
   if (peer == ctx->rank) return FMOE_OK;
-  FMOE_CUDA(cudaSetDevice(ctx->device));
+  ScopedDevice on_device(ctx->device);
+  FMOE_CUDA(on_device.err);
   cudaIpcMemHandle_t h;
   std::memcpy(&h, handle, sizeof(h));
   void* base = nullptr;
@@ -601,7 +621,7 @@ int fmoe_debug_buffer(fmoe_ctx* ctx, int32_t which, void** ptr_out, size_t* byte
 
 int fmoe_ctx_destroy(fmoe_ctx* ctx, void* stream) {
   if (ctx == nullptr) return FMOE_OK;
-  cudaSetDevice(ctx->device);
+  ScopedDevice on_device(ctx->device);
   cudaStreamSynchronize(static_cast<cudaStream_t>(stream));
   free_ctx(ctx);
   return FMOE_OK;
@@ -722,7 +742,8 @@ int fmoe_ctx_load_specialised(fmoe_ctx* ctx, const char* path) {
     return set_error(FMOE_ERR_INVALID_ARG, std::string(path) + " was built for another layer description (or another "
                                            "version of the library)");
   }
-  cudaError_t ce = cudaSetDevice(ctx->device);
+  ScopedDevice on_device(ctx->device);
+  cudaError_t ce = on_device.err;
   if (ce == cudaSuccess) ce = static_cast<cudaError_t>(prepare(static_cast<size_t>(ctx->geo.smem_bytes)));
   if (ce != cudaSuccess) {
     dlclose(h);
@@ -762,7 +783,8 @@ int fmoe_router_create(const fmoe_model_desc* model, int32_t device_id, int32_t 
   fmoe_router* r = new (std::nothrow) fmoe_router();
   if (r == nullptr) return set_error(FMOE_ERR_NO_MEMORY, "host allocation failed");
   r->model = *model; r->device = device_id; r->return_logits = return_logits;
-  cudaError_t ce = cudaSetDevice(device_id);
+  ScopedDevice on_device(device_id);
+  cudaError_t ce = on_device.err;
   const size_t n = static_cast<size_t>(model->tokens_per_rank) * model->top_k;
   if (ce == cudaSuccess) ce = cudaMalloc(&r->topk_idx, n * sizeof(int32_t));
   if (ce == cudaSuccess) ce = cudaMalloc(&r->topk_w, n * sizeof(float));
@@ -807,7 +829,7 @@ int fmoe_router_forward(fmoe_router* router, fmoe_ctx* moe, const fmoe_router_ar
 
 int fmoe_router_destroy(fmoe_router* router, void* stream) {
   if (router == nullptr) return FMOE_OK;
-  cudaSetDevice(router->device);
+  ScopedDevice on_device(router->device);
   cudaStreamSynchronize(static_cast<cudaStream_t>(stream));
   cudaFree(router->topk_idx);
   cudaFree(router->topk_w);
@@ -823,7 +845,8 @@ int fmoe_forward_host(fmoe_ctx* ctx, fmoe_router* router, const void* tokens_hos
   const size_t bytes = static_cast<size_t>(ctx->params.S) * ctx->params.H * ctx->eb;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (ctx->stage_tokens == nullptr) {
-    FMOE_CUDA(cudaSetDevice(ctx->device));
+    ScopedDevice on_device(ctx->device);
+    FMOE_CUDA(on_device.err);
     FMOE_CUDA(cudaMalloc(&ctx->stage_tokens, bytes));
     FMOE_CUDA(cudaMalloc(&ctx->stage_out, bytes));
   }
@@ -851,7 +874,8 @@ int fmoe_forward_host_async(fmoe_ctx* ctx, fmoe_router* router, const void* toke
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   fmoe_ctx::Pipe& pp = ctx->pipe;
   if (!pp.ready) {
-    FMOE_CUDA(cudaSetDevice(ctx->device));
+    ScopedDevice on_device(ctx->device);
+    FMOE_CUDA(on_device.err);
     FMOE_CUDA(cudaStreamCreateWithFlags(&pp.s_in, cudaStreamNonBlocking));
     FMOE_CUDA(cudaStreamCreateWithFlags(&pp.s_out, cudaStreamNonBlocking));
     for (int i = 0; i < 2; ++i) {

@@ -159,7 +159,10 @@ int fmoe_ctx_destroy(fmoe_ctx* ctx, void* stream);
 
 /* Replaces moe::forwardHost / moe_forward (moe.cuh:255-260; flashmoe/bindings.py:112-140):
  * one launch of the persistent kernel (dispatch, expert GEMMs, combine) on `stream`.
- * Every rank of the group must call it the same number of times.
+ * Every rank of the group must call it the same number of times.  `stream` belongs to the
+ * context's device, and that device is the calling thread's current one, as for any launch
+ * (the calls that create, map or destroy things make the device current themselves and put the
+ * caller's back before they return).
  * One context serves every layer of a model that shares this description: forwards on a
  * stream are ordered, the epoch protocol needs nothing cleared between them, and the TMA
  * descriptors of up to FMOE_LAYER_CACHE distinct (up, up_v, down) weight sets are kept, so
